@@ -1,0 +1,535 @@
+// Persistent, warp-specialised BF16 GEMM for sm_100a:  D[Md,Nd] = X[Md,K] * Y[Nd,K]^T,
+// X and Y K-major bf16, fp32 accumulation in tensor memory, bf16 (round-to-nearest-even) result.
+//
+// It computes what the reference's gemmkernel computes per 64x64 tile with wgmma
+// (neogemmV02.cu:179-260) and what its tcgen05 sketches intended (nemgemmV03.cu:208-341), but is
+// organised for Blackwell:
+//   warp 0      TMA producer: one lane streams 128B-swizzled K-major boxes of X and Y into a
+//               kStages-deep shared-memory ring, signalling full[] mbarriers by byte count;
+//   warp 1      UMMA issuer: one lane (of the leader CTA when two CTAs share a tile) issues
+//               tcgen05.mma into one of two TMEM accumulators and releases ring slots / publishes
+//               finished accumulators with tcgen05.commit;
+//   warps 2-5   epilogue: tcgen05.ld -> bf16 -> swizzled shared staging -> TMA store (or direct
+//               strided global stores), overlapped with the next tile's main loop through the
+//               second accumulator.
+// With kCtaGroup == 2 a cluster of two CTAs computes a (256 x BLOCK_N) tile: each CTA loads its
+// own 128 rows of X and its own half of the Y tile (plain per-CTA TMA loads whose byte counts
+// are credited to the leader's barrier), and the leader's MMA reads both halves.
+//
+// Work is handed out as segments (tile, first k-block, k-block count).  In the data-parallel
+// schedule every segment is a whole tile.  In the stream-K schedule (skinny, HBM-bound shapes) the
+// (tile x k-block) space is cut into equal contiguous ranges, one per CTA, so every SM streams the
+// same number of bytes; tiles cut by a range boundary are finished by whichever contributor
+// arrives last, which sums the fp32 partials in a fixed order.
+//
+// Every mbarrier wait is bounded (ptx::mbar_wait).  On expiry the role records a code in
+// `params.status`, raises the CTA's abort flag and falls through to the common tear-down, which
+// lets copies in flight land and frees tensor memory.  The kernel never traps or spins forever.
+#pragma once
+
+#include "ptx.cuh"
+
+namespace neogemm {
+
+enum EpilogueMode : int {
+  kEpiTmaStore = 0,  // row-major D, 16-byte-aligned pitch: staged through swizzled smem + TMA store
+  kEpiDirect = 1,    // arbitrary (row, col) strides straight from registers, bounds-checked
+};
+
+// Device-side error codes written to the status word (first error wins).
+enum DeviceError : int {
+  kDevOk = 0,
+  kDevTimeoutProducer = 1,   // TMA warp gave up waiting for a free ring slot
+  kDevTimeoutMmaFull = 2,    // MMA warp gave up waiting for operand bytes
+  kDevTimeoutMmaTmem = 3,    // MMA warp gave up waiting for a drained accumulator
+  kDevTimeoutEpilogue = 4,   // epilogue gave up waiting for a finished accumulator
+  kDevTmemAddress = 5,       // tensor-memory allocation did not start at column 0 (pair mode)
+};
+
+struct GemmParams {
+  int Md, Nd, K;
+  int num_m_tiles, num_n_tiles, num_tiles, num_k_blocks;
+  int group_m;               // tile rows per raster group (L2 reuse)
+  // Direct epilogue / split partials.
+  __nv_bfloat16* out;
+  long long out_stride_r, out_stride_c;
+  // Stream-K (zero / null in the data-parallel schedule).
+  int stream_k;              // 1: CTA c owns units [c*U/G, (c+1)*U/G) of the (tile x k-block) space
+  int max_contrib;           // partial slots per tile in `partials`
+  float* partials;           // [num_tiles][max_contrib][BLOCK_N][TILE_M] fp32
+  int* tile_counters;        // [num_tiles][kCtaGroup][4], zero before launch; the last arriver
+                             // of each entry re-zeroes it
+  // Error reporting: status[0] = code, [1] = blockIdx, [2] = segment index, [3] = stage / acc.
+  int* status;
+};
+
+template <int kCtaGroup_, int BLOCK_N_, int kStages_, int kEpiMode_>
+struct GemmConfig {
+  static constexpr int kCtaGroup = kCtaGroup_;
+  static constexpr int BLOCK_N = BLOCK_N_;           // UMMA N = tile columns
+  static constexpr int kStages = kStages_;
+  static constexpr int kEpiMode = kEpiMode_;
+  static constexpr int BLOCK_M = 128;                 // rows of X (TMEM lanes) per CTA
+  static constexpr int TILE_M = BLOCK_M * kCtaGroup;  // UMMA M
+  static constexpr int BLOCK_K = 64;                  // 64 bf16 = one 128-byte swizzle row
+  static constexpr int UMMA_K = 16;
+  static constexpr int LOAD_N = BLOCK_N / kCtaGroup;  // rows of Y each CTA fetches
+  static constexpr int SMEM_X = BLOCK_M * BLOCK_K * 2;
+  static constexpr int SMEM_Y = LOAD_N * BLOCK_K * 2;
+  static constexpr int SMEM_STAGE = SMEM_X + SMEM_Y;
+  static constexpr int EPI_COLS = 64;                 // columns per TMA-store box (128 B of bf16)
+  static constexpr int SMEM_EPI_WARP_BUF = 32 * EPI_COLS * 2;  // 4 KB: 32 rows x 128 B
+  static constexpr int kEpiBufs = 2;
+  static constexpr int SMEM_EPI = (kEpiMode == kEpiTmaStore) ? 4 * kEpiBufs * SMEM_EPI_WARP_BUF : 0;
+  static constexpr int SMEM_BARRIERS = (2 * kStages + 4) * 8 + 16;
+  // +1024: the ring must start on a 1024-byte boundary for the 128-byte swizzle.
+  static constexpr int SMEM_TOTAL = kStages * SMEM_STAGE + SMEM_EPI + SMEM_BARRIERS + 1024;
+  static constexpr int kAccumCols = BLOCK_N;          // fp32 columns per accumulator
+  static constexpr int kTmemCols = (kCtaGroup == 2) ? 512
+      : (2 * BLOCK_N <= 32) ? 32 : (2 * BLOCK_N <= 64) ? 64 : (2 * BLOCK_N <= 128) ? 128
+      : (2 * BLOCK_N <= 256) ? 256 : 512;
+  static constexpr int kThreads = 192;
+  static_assert(BLOCK_N % 16 == 0 && BLOCK_N >= 16 && BLOCK_N <= 256, "UMMA N");
+  static_assert(SMEM_Y % 1024 == 0 || kStages == 1 || (SMEM_STAGE % 1024 == 0), "swizzle align");
+  static_assert(SMEM_STAGE % 1024 == 0, "every stage must keep 1024-byte alignment");
+  static_assert(kEpiMode == kEpiDirect || BLOCK_N % EPI_COLS == 0, "TMA-store boxes are 64 wide");
+  static_assert(kCtaGroup == 1 || kTmemCols == 512,
+                "pair mode allocates all of tensor memory so both CTAs get column 0");
+  static_assert(SMEM_TOTAL <= 232448, "exceeds 227 KB of shared memory per CTA");
+};
+
+// One unit of work for a CTA (pair).
+struct Segment {
+  int tile;       // linear tile index
+  int kb_begin;   // first k-block
+  int kb_count;   // k-blocks in this segment (>= 1)
+  int contrib;    // index of this segment among the tile's contributors (0 if whole)
+  int n_contrib;  // contributors of this tile (1 if whole)
+};
+
+// Enumerates this CTA's segments.  Every role constructs one and walks the same sequence.
+struct SegmentIter {
+  int stream_k, num_tiles, num_k_blocks;
+  // data-parallel
+  int next_tile, tile_step;
+  // stream-K
+  long long u, u_end, total_units;
+  int num_ctas;
+
+  __device__ __forceinline__ SegmentIter(const GemmParams& p, int worker, int num_workers) {
+    stream_k = p.stream_k;
+    num_tiles = p.num_tiles;
+    num_k_blocks = p.num_k_blocks;
+    next_tile = worker;
+    tile_step = num_workers;
+    num_ctas = num_workers;
+    total_units = static_cast<long long>(p.num_tiles) * p.num_k_blocks;
+    u = range_start(worker);
+    u_end = range_start(worker + 1);
+  }
+
+  __device__ __forceinline__ long long range_start(int c) const {
+    return (total_units * c) / num_ctas;
+  }
+
+  // Index of the CTA whose range holds unit `x`.
+  __device__ __forceinline__ int owner_of(long long x) const {
+    int c = static_cast<int>((x * num_ctas) / total_units);
+    while (c + 1 < num_ctas && range_start(c + 1) <= x) ++c;
+    while (c > 0 && range_start(c) > x) --c;
+    return c;
+  }
+
+  __device__ __forceinline__ bool next(Segment& s) {
+    if (!stream_k) {
+      if (next_tile >= num_tiles) return false;
+      s.tile = next_tile;
+      s.kb_begin = 0;
+      s.kb_count = num_k_blocks;
+      s.contrib = 0;
+      s.n_contrib = 1;
+      next_tile += tile_step;
+      return true;
+    }
+    if (u >= u_end) return false;
+    const int tile = static_cast<int>(u / num_k_blocks);
+    const long long tile_u0 = static_cast<long long>(tile) * num_k_blocks;
+    const long long tile_u1 = tile_u0 + num_k_blocks;
+    const long long seg_end = tile_u1 < u_end ? tile_u1 : u_end;
+    s.tile = tile;
+    s.kb_begin = static_cast<int>(u - tile_u0);
+    s.kb_count = static_cast<int>(seg_end - u);
+    if (s.kb_count == num_k_blocks) {
+      s.contrib = 0;
+      s.n_contrib = 1;
+    } else {
+      const int first = owner_of(tile_u0);
+      const int last = owner_of(tile_u1 - 1);
+      s.contrib = owner_of(u) - first;
+      s.n_contrib = last - first + 1;
+    }
+    u = seg_end;
+    return true;
+  }
+};
+
+// Grouped raster: consecutive tile ids walk down `group_m` tile rows before moving one tile
+// column to the right, so the tiles in flight at any moment share a few row panels of X and a
+// few column panels of Y in L2.  (The reference rasters row-major, neogemmV02.cu:190-191.)
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& tm, int& tn) {
+  const int group_size = p.group_m * p.num_n_tiles;
+  const int group = tile / group_size;
+  const int first_m = group * p.group_m;
+  const int rows = min(p.group_m, p.num_m_tiles - first_m);
+  const int local = tile - group * group_size;
+  tm = first_m + local % rows;
+  tn = local / rows;
+}
+
+__device__ __forceinline__ void report_error(const GemmParams& p, volatile int* abort_flag,
+                                             int code, int seg, int aux) {
+  *abort_flag = 1;
+  if (p.status != nullptr && atomicCAS(p.status, 0, code) == 0) {
+    p.status[1] = static_cast<int>(blockIdx.x);
+    p.status[2] = seg;
+    p.status[3] = aux;
+    __threadfence_system();
+  }
+}
+
+template <class Cfg>
+__global__ void __launch_bounds__(Cfg::kThreads, 1)
+gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
+                    const __grid_constant__ CUtensorMap tmap_y,
+                    const __grid_constant__ CUtensorMap tmap_d,
+                    const GemmParams p) {
+  using namespace ptx;
+  constexpr int kCtaGroup = Cfg::kCtaGroup;
+  constexpr int BLOCK_N = Cfg::BLOCK_N;
+  constexpr int kStages = Cfg::kStages;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+
+  const uint32_t ring = smem_base;
+  const uint32_t epi_base = ring + kStages * Cfg::SMEM_STAGE;
+  const uint32_t bar_base = epi_base + Cfg::SMEM_EPI;
+  const uint32_t full_bar = bar_base;                       // [kStages]
+  const uint32_t empty_bar = full_bar + 8 * kStages;        // [kStages]
+  const uint32_t tmem_full_bar = empty_bar + 8 * kStages;   // [2]
+  const uint32_t tmem_empty_bar = tmem_full_bar + 16;       // [2]
+  const uint32_t tmem_slot = tmem_empty_bar + 16;           // u32
+  uint8_t* tail_gen = smem_gen + (tmem_slot - smem_base);
+  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(tail_gen);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tail_gen + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const uint32_t lane = lane_id();
+  const uint32_t cta_rank = (kCtaGroup == 2) ? cluster_ctarank() : 0u;
+  const bool is_leader = (cta_rank == 0);
+  const int worker = static_cast<int>(blockIdx.x) / kCtaGroup;
+  const int num_workers = static_cast<int>(gridDim.x) / kCtaGroup;
+
+  // ---------------------------------------------------------------- set-up
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full_bar + 8 * s, 1);   // one arrive.expect_tx per phase (leader's producer)
+      mbar_init(empty_bar + 8 * s, 1);  // one tcgen05.commit per phase
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tmem_full_bar + 8 * a, 1);               // one tcgen05.commit per tile
+      mbar_init(tmem_empty_bar + 8 * a, 4 * kCtaGroup);  // one arrive per epilogue warp
+    }
+    fence_barrier_init();
+  }
+  if (warp == 0 && lane == 0) {
+    prefetch_tensormap(&tmap_x);
+    prefetch_tensormap(&tmap_y);
+    if (Cfg::kEpiMode == kEpiTmaStore) prefetch_tensormap(&tmap_d);
+  }
+  if (warp == 1) {
+    tmem_alloc<1>(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish<1>();
+  }
+  tcgen05_fence_before();
+  if (kCtaGroup == 2) cluster_sync_all(); else __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot_gen;
+  if (kCtaGroup == 2 && tmem_base != 0 && threadIdx.x == 0) {
+    // The pair's MMA addresses both CTAs' tensor memory with the leader's address.
+    report_error(p, abort_flag, kDevTmemAddress, 0, static_cast<int>(tmem_base));
+  }
+  if (kCtaGroup == 2) __syncthreads();
+
+  // ---------------------------------------------------------------- roles
+  if (warp == 0) {
+    // ======================= TMA producer =======================
+    if (lane == 0 && *abort_flag == 0) {
+      SegmentIter it(p, worker, num_workers);
+      Segment seg;
+      uint32_t stage = 0, phase = 0;
+      int seg_idx = 0;
+      const uint32_t leader_full = (kCtaGroup == 2) ? mapa_u32(full_bar, 0) : full_bar;
+      bool ok = true;
+      while (ok && it.next(seg)) {
+        int tm, tn;
+        tile_coords(p, seg.tile, tm, tn);
+        const int row_x = tm * Cfg::TILE_M + static_cast<int>(cta_rank) * Cfg::BLOCK_M;
+        const int row_y = tn * BLOCK_N + static_cast<int>(cta_rank) * Cfg::LOAD_N;
+        for (int kb = seg.kb_begin; kb < seg.kb_begin + seg.kb_count; ++kb) {
+          if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1, abort_flag)) {
+            report_error(p, abort_flag, kDevTimeoutProducer, seg_idx, static_cast<int>(stage));
+            ok = false;
+            break;
+          }
+          const uint32_t sx = ring + stage * Cfg::SMEM_STAGE;
+          const uint32_t sy = sx + Cfg::SMEM_X;
+          if (kCtaGroup == 1) {
+            mbar_arrive_expect_tx(full_bar + 8 * stage, Cfg::SMEM_STAGE);
+            tma_load_2d(sx, &tmap_x, full_bar + 8 * stage, kb * Cfg::BLOCK_K, row_x);
+            tma_load_2d(sy, &tmap_y, full_bar + 8 * stage, kb * Cfg::BLOCK_K, row_y);
+          } else {
+            if (is_leader) mbar_arrive_expect_tx(full_bar + 8 * stage, 2 * Cfg::SMEM_STAGE);
+            tma_load_2d_pair(sx, &tmap_x, leader_full + 8 * stage, kb * Cfg::BLOCK_K, row_x);
+            tma_load_2d_pair(sy, &tmap_y, leader_full + 8 * stage, kb * Cfg::BLOCK_K, row_y);
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+        ++seg_idx;
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ======================= UMMA issuer (leader CTA only) =======================
+    if (lane == 0 && is_leader && *abort_flag == 0) {
+      SegmentIter it(p, worker, num_workers);
+      Segment seg;
+      uint32_t stage = 0, phase = 0;
+      int seg_idx = 0;
+      constexpr uint32_t idesc = make_idesc_bf16(Cfg::TILE_M, BLOCK_N);
+      const uint32_t peer_empty = (kCtaGroup == 2) ? mapa_u32(empty_bar, 1) : 0u;
+      const uint32_t peer_tmem_full = (kCtaGroup == 2) ? mapa_u32(tmem_full_bar, 1) : 0u;
+      bool ok = true;
+      while (ok && it.next(seg)) {
+        const uint32_t acc = seg_idx & 1, acc_phase = (seg_idx >> 1) & 1;
+        if (!mbar_wait<kCtaGroup == 2>(tmem_empty_bar + 8 * acc, acc_phase ^ 1, abort_flag)) {
+          report_error(p, abort_flag, kDevTimeoutMmaTmem, seg_idx, static_cast<int>(acc));
+          break;
+        }
+        tcgen05_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * Cfg::kAccumCols;
+        for (int kb = 0; kb < seg.kb_count; ++kb) {
+          if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag)) {
+            report_error(p, abort_flag, kDevTimeoutMmaFull, seg_idx, static_cast<int>(stage));
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after();
+          const uint32_t sx = ring + stage * Cfg::SMEM_STAGE;
+          const uint64_t desc_x = make_smem_desc_sw128(sx);
+          const uint64_t desc_y = make_smem_desc_sw128(sx + Cfg::SMEM_X);
+#pragma unroll
+          for (int k = 0; k < Cfg::BLOCK_K / Cfg::UMMA_K; ++k) {
+            // +32 bytes (two 16-byte units) per 16-element K step inside the swizzle row.
+            umma_bf16<kCtaGroup>(tmem_d, desc_x + 2 * k, desc_y + 2 * k, idesc,
+                                 (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit<kCtaGroup>(empty_bar + 8 * stage);
+          if (kCtaGroup == 2) umma_commit<kCtaGroup>(peer_empty + 8 * stage);
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit<kCtaGroup>(tmem_full_bar + 8 * acc);
+        if (kCtaGroup == 2) umma_commit<kCtaGroup>(peer_tmem_full + 8 * acc);
+        ++seg_idx;
+      }
+    }
+    __syncwarp();
+  } else {
+    // ======================= epilogue (warps 2..5) =======================
+    const uint32_t quad = warp & 3;               // TMEM lane quadrant this warp may read
+    const int row_in_cta = quad * 32 + lane;      // accumulator row owned by this thread
+    const uint32_t leader_tmem_empty = (kCtaGroup == 2) ? mapa_u32(tmem_empty_bar, 0) : 0u;
+    SegmentIter it(p, worker, num_workers);
+    Segment seg;
+    int seg_idx = 0;
+    uint32_t store_count = 0;
+    bool ok = (*abort_flag == 0);
+    while (ok && it.next(seg)) {
+      const uint32_t acc = seg_idx & 1, acc_phase = (seg_idx >> 1) & 1;
+      bool got = mbar_wait(tmem_full_bar + 8 * acc, acc_phase, abort_flag);
+      got = __all_sync(0xffffffffu, got);
+      if (!got) {
+        if (lane == 0) report_error(p, abort_flag, kDevTimeoutEpilogue, seg_idx, static_cast<int>(acc));
+        break;
+      }
+      tcgen05_fence_after();
+      int tm, tn;
+      tile_coords(p, seg.tile, tm, tn);
+      const int row0 = tm * Cfg::TILE_M + static_cast<int>(cta_rank) * Cfg::BLOCK_M;
+      const int col0 = tn * BLOCK_N;
+      const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + acc * Cfg::kAccumCols;
+
+      // ---- stream-K: publish this segment's partial; the last arriver finishes the rows ----
+      bool finish = true;
+      const float* tile_partials = nullptr;
+      if constexpr (Cfg::kEpiMode == kEpiDirect) {
+        if (seg.n_contrib > 1) {
+          // Slot layout [contributor][column][row] so that a warp's 32 rows of one column are
+          // one 128-byte line.  Counters are per (tile, CTA of the pair, lane quadrant): the
+          // four epilogue warps never have to synchronise with each other.
+          tile_partials = p.partials + static_cast<size_t>(seg.tile) * p.max_contrib *
+                                           (static_cast<size_t>(BLOCK_N) * Cfg::TILE_M);
+          float* mine = const_cast<float*>(tile_partials) +
+                        static_cast<size_t>(seg.contrib) * BLOCK_N * Cfg::TILE_M +
+                        cta_rank * Cfg::BLOCK_M + row_in_cta;
+#pragma unroll 1
+          for (int c = 0; c < BLOCK_N; c += 16) {
+            uint32_t r[16];
+            tmem_ld_32x32b_x16(taddr + c, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              __stcg(mine + static_cast<size_t>(c + j) * Cfg::TILE_M, __uint_as_float(r[j]));
+          }
+          __threadfence();
+          __syncwarp();
+          int* counter = p.tile_counters + (seg.tile * kCtaGroup + static_cast<int>(cta_rank)) * 4 + quad;
+          int prev = 0;
+          if (lane == 0) prev = atomicAdd(counter, 1);
+          prev = __shfl_sync(0xffffffffu, prev, 0);
+          finish = (prev == seg.n_contrib - 1);
+          if (finish) {
+            __threadfence();
+            if (lane == 0) *counter = 0;  // ready for the next launch that uses this workspace
+          }
+        }
+      }
+
+      if (!finish) {
+        // nothing to store: another contributor completes these rows
+      } else
+      if (Cfg::kEpiMode == kEpiTmaStore) {
+        const uint32_t warp_stage = epi_base + (warp - 2) * Cfg::kEpiBufs * Cfg::SMEM_EPI_WARP_BUF;
+        const int my_row0 = row0 + quad * 32;
+#pragma unroll 1
+        for (int c = 0; c < BLOCK_N; c += Cfg::EPI_COLS) {
+          const uint32_t buf = warp_stage + (store_count % Cfg::kEpiBufs) * Cfg::SMEM_EPI_WARP_BUF;
+          // The store issued kEpiBufs boxes ago read from this buffer; make sure it is done.
+          if (lane == 0) tma_store_wait_read<Cfg::kEpiBufs - 1>();
+          __syncwarp();
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32b_x32(taddr + c, r0);
+          tmem_ld_32x32b_x32(taddr + c + 32, r1);
+          tmem_ld_wait();
+          const uint32_t row_addr = buf + lane * 128u;
+          const uint32_t sw = lane & 7u;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            st_shared_v4(row_addr + ((static_cast<uint32_t>(j) ^ sw) << 4),
+                         pack_bf16x2(__uint_as_float(r0[8 * j + 0]), __uint_as_float(r0[8 * j + 1])),
+                         pack_bf16x2(__uint_as_float(r0[8 * j + 2]), __uint_as_float(r0[8 * j + 3])),
+                         pack_bf16x2(__uint_as_float(r0[8 * j + 4]), __uint_as_float(r0[8 * j + 5])),
+                         pack_bf16x2(__uint_as_float(r0[8 * j + 6]), __uint_as_float(r0[8 * j + 7])));
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            st_shared_v4(row_addr + ((static_cast<uint32_t>(j + 4) ^ sw) << 4),
+                         pack_bf16x2(__uint_as_float(r1[8 * j + 0]), __uint_as_float(r1[8 * j + 1])),
+                         pack_bf16x2(__uint_as_float(r1[8 * j + 2]), __uint_as_float(r1[8 * j + 3])),
+                         pack_bf16x2(__uint_as_float(r1[8 * j + 4]), __uint_as_float(r1[8 * j + 5])),
+                         pack_bf16x2(__uint_as_float(r1[8 * j + 6]), __uint_as_float(r1[8 * j + 7])));
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (my_row0 < p.Md && col0 + c < p.Nd) tma_store_2d(&tmap_d, buf, col0 + c, my_row0);
+            tma_store_commit();
+          }
+          ++store_count;
+        }
+      } else {
+        const int row = row0 + row_in_cta;
+        __nv_bfloat16* out_row = p.out + static_cast<long long>(row) * p.out_stride_r;
+        const bool vec_ok = (p.out_stride_c == 1) && ((p.out_stride_r & 7) == 0) &&
+                            ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+#pragma unroll 1
+        for (int c = 0; c < BLOCK_N; c += 16) {
+          uint32_t r[16];
+          tmem_ld_32x32b_x16(taddr + c, r);
+          tmem_ld_wait();
+          if (tile_partials != nullptr) {
+            // Sum the contributors in index order (own value from tensor memory) so the result
+            // does not depend on which contributor arrived last.
+            const float* col_base = tile_partials + static_cast<size_t>(c) * Cfg::TILE_M +
+                                    cta_rank * Cfg::BLOCK_M + row_in_cta;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float own = __uint_as_float(r[j]);
+              float v = 0.f;
+              for (int q = 0; q < seg.n_contrib; ++q) {
+                const float t = (q == seg.contrib)
+                    ? own
+                    : __ldcg(col_base + (static_cast<size_t>(q) * BLOCK_N + j) * Cfg::TILE_M);
+                v = (q == 0) ? t : v + t;
+              }
+              r[j] = __float_as_uint(v);
+            }
+          }
+          const int col = col0 + c;
+          if (row < p.Md && col < p.Nd) {
+            if (vec_ok && col + 16 <= p.Nd) {
+              uint4 v0, v1;
+              v0.x = pack_bf16x2(__uint_as_float(r[0]), __uint_as_float(r[1]));
+              v0.y = pack_bf16x2(__uint_as_float(r[2]), __uint_as_float(r[3]));
+              v0.z = pack_bf16x2(__uint_as_float(r[4]), __uint_as_float(r[5]));
+              v0.w = pack_bf16x2(__uint_as_float(r[6]), __uint_as_float(r[7]));
+              v1.x = pack_bf16x2(__uint_as_float(r[8]), __uint_as_float(r[9]));
+              v1.y = pack_bf16x2(__uint_as_float(r[10]), __uint_as_float(r[11]));
+              v1.z = pack_bf16x2(__uint_as_float(r[12]), __uint_as_float(r[13]));
+              v1.w = pack_bf16x2(__uint_as_float(r[14]), __uint_as_float(r[15]));
+              *reinterpret_cast<uint4*>(out_row + col) = v0;
+              *reinterpret_cast<uint4*>(out_row + col + 8) = v1;
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                if (col + j < p.Nd)
+                  out_row[static_cast<long long>(col + j) * p.out_stride_c] =
+                      __float2bfloat16_rn(__uint_as_float(r[j]));
+              }
+            }
+          }
+        }
+      }
+
+      // Accumulator drained: hand it back to the MMA warp (one arrive per warp).
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (kCtaGroup == 2) mbar_arrive_cluster(leader_tmem_empty + 8 * acc);
+        else mbar_arrive(tmem_empty_bar + 8 * acc);
+      }
+      ++seg_idx;
+    }
+    if (Cfg::kEpiMode == kEpiTmaStore && lane == 0) tma_store_wait_all<0>();
+    __syncwarp();
+  }
+
+  // ---------------------------------------------------------------- tear-down
+  tcgen05_fence_before();
+  if (kCtaGroup == 2) cluster_sync_all(); else __syncthreads();
+  if (*abort_flag != 0) {
+    // Let TMA boxes still in flight land in this CTA's shared memory before it is released.
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 1000000ull) __nanosleep(1000);
+    if (kCtaGroup == 2) cluster_sync_all(); else __syncthreads();
+  }
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc<1>(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+}  // namespace neogemm

@@ -1,0 +1,641 @@
+// Host launcher and C ABI of libneogemm.so (declarations and contracts: include/neogemm.h).
+//
+// Replaces the reference's host function neoGemmV1 (nemgemmV03.cu:343-391) and its tensor-map
+// helpers (nemgemmV03.cu:32-68).  Differences that matter to a caller:
+//   * tensor maps are built on the host and passed to the kernel as __grid_constant__ parameters;
+//     nothing is cudaMalloc'ed or copied per call (the reference copies each map into device
+//     memory, nemgemmV03.cu:60-68) and the cache is keyed by pointer and geometry, not by shape
+//     alone (nemgemmV03.cu:359);
+//   * arguments are validated and failures come back as status codes (the reference's asserts
+//     are compiled out, setup.py:15);
+//   * the launch goes to the caller's stream.
+// No torch headers here: this file is compiled by nvcc alone and linked with the static CUDA
+// runtime; the driver's cuTensorMapEncodeTiled is looked up at run time so the library loads on
+// machines without a GPU driver (where every compute entry point reports an error).
+#include "../../include/neogemm.h"
+
+#include <cuda_runtime.h>
+#include <cudaTypedefs.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <vector>
+
+#include "gemm_sm100.cuh"
+
+namespace neogemm {
+namespace {
+
+constexpr int kMaxDevices = 64;
+
+// ------------------------------------------------------------------------------------------
+// Kernel table
+// ------------------------------------------------------------------------------------------
+struct KernelEntry {
+  int cta_group, block_n, stages, epi;
+  const void* fn;
+  int smem_bytes;
+  int tmem_cols;
+};
+
+template <class Cfg>
+KernelEntry make_entry() {
+  return KernelEntry{Cfg::kCtaGroup, Cfg::BLOCK_N, Cfg::kStages, Cfg::kEpiMode,
+                     reinterpret_cast<const void*>(&gemm_bf16_nt_kernel<Cfg>), Cfg::SMEM_TOTAL,
+                     Cfg::kTmemCols};
+}
+
+// Stage counts fill the 227 KB of shared memory; a CTA that owns more than half of it is alone on
+// its SM, which is what makes its tensor-memory allocation safe from starvation.
+const KernelEntry* kernel_table(int* count) {
+  static const KernelEntry table[] = {
+      make_entry<GemmConfig<1, 256, 4, kEpiTmaStore>>(),
+      make_entry<GemmConfig<1, 128, 6, kEpiTmaStore>>(),
+      make_entry<GemmConfig<2, 256, 6, kEpiTmaStore>>(),
+      make_entry<GemmConfig<2, 128, 8, kEpiTmaStore>>(),
+      make_entry<GemmConfig<1, 256, 4, kEpiDirect>>(),
+      make_entry<GemmConfig<1, 128, 7, kEpiDirect>>(),
+      make_entry<GemmConfig<1, 64, 9, kEpiDirect>>(),
+      make_entry<GemmConfig<1, 32, 11, kEpiDirect>>(),
+      make_entry<GemmConfig<1, 16, 12, kEpiDirect>>(),
+  };
+  *count = static_cast<int>(sizeof(table) / sizeof(table[0]));
+  return table;
+}
+
+const KernelEntry* find_kernel(int cta_group, int block_n, int epi, int* index) {
+  int n;
+  const KernelEntry* t = kernel_table(&n);
+  for (int i = 0; i < n; ++i) {
+    if (t[i].cta_group == cta_group && t[i].block_n == block_n && t[i].epi == epi) {
+      if (index) *index = i;
+      return &t[i];
+    }
+  }
+  return nullptr;
+}
+
+// ------------------------------------------------------------------------------------------
+// Per-device state
+// ------------------------------------------------------------------------------------------
+struct DeviceState {
+  bool ready = false;
+  int init_error = NEOGEMM_OK;
+  int sm_count = 0;
+  int* status_host = nullptr;  // mapped pinned memory: the kernel writes, the host reads
+  int* status_dev = nullptr;
+  void* workspace = nullptr;   // library-owned stream-K scratch
+  size_t workspace_bytes = 0;
+  void* stage[3] = {nullptr, nullptr, nullptr};  // device copies of A, B, C for the host entry
+  size_t stage_bytes[3] = {0, 0, 0};
+  bool attr_done[16] = {};
+};
+
+DeviceState g_dev[kMaxDevices];
+std::mutex g_mu;
+PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
+bool g_encode_looked_up = false;
+
+struct Override {
+  int cta_group = -1, block_n = -1, swap = -1, stream_k = -1, group_m = -1, max_ctas = -1;
+};
+thread_local Override t_override;
+thread_local int t_last_config[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+
+// Must be called with g_mu held.  Returns the state of the current device or nullptr + code.
+DeviceState* device_state(int* code) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    cudaGetLastError();
+    *code = NEOGEMM_ERR_UNSUPPORTED;
+    return nullptr;
+  }
+  DeviceState& st = g_dev[dev];
+  if (st.ready) {
+    *code = st.init_error;
+    return st.init_error == NEOGEMM_OK ? &st : nullptr;
+  }
+  st.ready = true;
+  int major = 0;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess ||
+      major != 10 ||
+      cudaDeviceGetAttribute(&st.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+    cudaGetLastError();
+    st.init_error = NEOGEMM_ERR_UNSUPPORTED;
+    *code = st.init_error;
+    return nullptr;
+  }
+  if (!g_encode_looked_up) {
+    g_encode_looked_up = true;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) ==
+            cudaSuccess && q == cudaDriverEntryPointSuccess) {
+      g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+    } else {
+      cudaGetLastError();
+    }
+  }
+  if (g_encode == nullptr) {
+    st.init_error = NEOGEMM_ERR_DESCRIPTOR;
+    *code = st.init_error;
+    return nullptr;
+  }
+  if (cudaHostAlloc(reinterpret_cast<void**>(&st.status_host), 64, cudaHostAllocMapped) !=
+          cudaSuccess ||
+      cudaHostGetDevicePointer(reinterpret_cast<void**>(&st.status_dev), st.status_host, 0) !=
+          cudaSuccess) {
+    cudaGetLastError();
+    st.init_error = NEOGEMM_ERR_CUDA;
+    *code = st.init_error;
+    return nullptr;
+  }
+  std::memset(st.status_host, 0, 64);
+  *code = NEOGEMM_OK;
+  return &st;
+}
+
+// ------------------------------------------------------------------------------------------
+// Tensor maps
+// ------------------------------------------------------------------------------------------
+struct MapKey {
+  const void* base;
+  uint64_t inner, rows, pitch_bytes;
+  uint32_t box_rows;
+  int for_store;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && inner == o.inner && rows == o.rows && pitch_bytes == o.pitch_bytes &&
+           box_rows == o.box_rows && for_store == o.for_store;
+  }
+};
+struct MapSlot {
+  MapKey key;
+  CUtensorMap map;
+};
+thread_local std::vector<MapSlot> t_map_cache;  // most recently used at the back
+constexpr size_t kMapCacheSize = 32;
+
+// Row-major bf16 matrix [rows, inner] with row pitch `pitch_bytes`; box = 64 elements (one
+// 128-byte swizzle row) x box_rows; out-of-range elements read as zero and are not written.
+// Same geometry family as the reference's create_tensor_map (nemgemmV03.cu:32-58), with the
+// box height following the tile instead of the fixed 64.
+int get_tensor_map(const void* base, uint64_t inner, uint64_t rows, uint64_t pitch_bytes,
+                   uint32_t box_rows, int for_store, CUtensorMap* out) {
+  const MapKey key{base, inner, rows, pitch_bytes, box_rows, for_store};
+  for (size_t i = t_map_cache.size(); i-- > 0;) {
+    if (t_map_cache[i].key == key) {
+      *out = t_map_cache[i].map;
+      return NEOGEMM_OK;
+    }
+  }
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (pitch_bytes & 15) != 0 ||
+      pitch_bytes >= (1ull << 40) || inner == 0 || rows == 0 || inner > 0xffffffffull ||
+      rows > 0xffffffffull || box_rows == 0 || box_rows > 256) {
+    return NEOGEMM_ERR_UNSUPPORTED;
+  }
+  cuuint64_t dims[2] = {inner, rows};
+  cuuint64_t strides[1] = {pitch_bytes};
+  cuuint32_t box[2] = {64, box_rows};
+  cuuint32_t elem_strides[2] = {1, 1};
+  CUtensorMap m;
+  const CUresult r = g_encode(
+      &m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+      elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+      for_store ? CU_TENSOR_MAP_L2_PROMOTION_NONE : CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return NEOGEMM_ERR_DESCRIPTOR;
+  if (t_map_cache.size() >= kMapCacheSize) t_map_cache.erase(t_map_cache.begin());
+  t_map_cache.push_back(MapSlot{key, m});
+  *out = m;
+  return NEOGEMM_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// Planning
+// ------------------------------------------------------------------------------------------
+struct Plan {
+  bool swap = false;        // X = the operand that indexes output COLUMNS of the stored matrix
+  int cta_group = 1, block_n = 256, epi = kEpiTmaStore;
+  bool stream_k = false;
+  int group_m = 8;
+  int num_ctas = 0;
+  int Md = 0, Nd = 0;
+  int num_m_tiles = 0, num_n_tiles = 0, num_tiles = 0, num_k_blocks = 0;
+  int max_contrib = 0;
+  size_t counters_bytes = 0, partials_bytes = 0;
+  const KernelEntry* kernel = nullptr;
+  int kernel_index = -1;
+};
+
+int round_block_n(int64_t n) {
+  if (n <= 16) return 16;
+  if (n <= 32) return 32;
+  if (n <= 64) return 64;
+  if (n <= 128) return 128;
+  return 256;
+}
+
+// pm x pn is the matrix as stored (row-major, pitch ldc): [M,N] for row-major C, [N,M] for the
+// reference's column-major C.
+int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int sm_count,
+              const Override& ov, Plan* plan) {
+  Plan p;
+  const bool tma_store_ok = (ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
+
+  // Orientation.  The 128-lane axis of the tensor core wants the long dimension.
+  bool swap = (pm <= 128 && pn > pm);
+  if (ov.swap >= 0) swap = (ov.swap != 0);
+  p.swap = swap;
+  const int64_t md = swap ? pn : pm;
+  const int64_t nd = swap ? pm : pn;
+  if (md > 0x7fffffffll || nd > 0x7fffffffll) return NEOGEMM_ERR_UNSUPPORTED;
+  p.Md = static_cast<int>(md);
+  p.Nd = static_cast<int>(nd);
+
+  int block_n = round_block_n(nd);
+  if (ov.block_n > 0) block_n = ov.block_n;
+  int cta_group = 1;
+  if (ov.cta_group > 0) cta_group = ov.cta_group;
+  int epi = kEpiDirect;
+  if (!swap && tma_store_ok && block_n >= 128) epi = kEpiTmaStore;
+  if (cta_group == 2 && (epi != kEpiTmaStore || block_n < 128)) cta_group = 1;
+  if (epi == kEpiTmaStore && block_n == 256 && ov.block_n < 0) {
+    // Fewer, larger tiles only when there are enough of them to fill the machine.
+    const int64_t tiles256 = ((md + 127) / 128) * ((nd + 255) / 256);
+    if (tiles256 < sm_count) block_n = 128;
+  }
+  p.block_n = block_n;
+  p.cta_group = cta_group;
+  p.epi = epi;
+  p.kernel = find_kernel(cta_group, block_n, epi, &p.kernel_index);
+  if (p.kernel == nullptr) return NEOGEMM_ERR_UNSUPPORTED;
+
+  const int tile_m = 128 * cta_group;
+  p.num_m_tiles = static_cast<int>((md + tile_m - 1) / tile_m);
+  p.num_n_tiles = static_cast<int>((nd + block_n - 1) / block_n);
+  const int64_t tiles = static_cast<int64_t>(p.num_m_tiles) * p.num_n_tiles;
+  if (tiles > 0x3fffffffll) return NEOGEMM_ERR_UNSUPPORTED;
+  p.num_tiles = static_cast<int>(tiles);
+  p.num_k_blocks = static_cast<int>((K + 63) / 64);
+
+  p.group_m = (cta_group == 2) ? 8 : 16;
+  if (ov.group_m > 0) p.group_m = ov.group_m;
+  p.group_m = std::max(1, std::min(p.group_m, p.num_m_tiles));
+
+  const int workers_max = std::max(1, sm_count / cta_group);
+  // Stream-K: only for the direct-store (skinny) kernels, when whole tiles cannot fill or
+  // balance the machine and there is enough K to cut.
+  bool stream_k = (epi == kEpiDirect) && (block_n <= 128) && (p.num_k_blocks >= 8) &&
+                  (p.num_tiles % workers_max != 0) && (p.num_tiles < 8 * workers_max);
+  if (ov.stream_k >= 0) stream_k = (ov.stream_k != 0) && (epi == kEpiDirect);
+  p.stream_k = stream_k;
+
+  int workers = workers_max;
+  if (ov.max_ctas > 0) workers = std::max(1, std::min(workers, ov.max_ctas / cta_group));
+  if (stream_k) {
+    const int64_t units = static_cast<int64_t>(p.num_tiles) * p.num_k_blocks;
+    workers = static_cast<int>(std::min<int64_t>(workers, units));
+    const int64_t per = units / workers;  // >= 1
+    p.max_contrib = static_cast<int>((p.num_k_blocks + per - 1) / per) + 1;
+    p.counters_bytes = ((static_cast<size_t>(p.num_tiles) * cta_group * 4 * sizeof(int)) + 255) &
+                       ~static_cast<size_t>(255);
+    p.partials_bytes = static_cast<size_t>(p.num_tiles) * p.max_contrib * block_n * tile_m *
+                       sizeof(float);
+  } else {
+    workers = std::min(workers, p.num_tiles);
+  }
+  p.num_ctas = workers * cta_group;
+  *plan = p;
+  return NEOGEMM_OK;
+}
+
+int validate(const void* A, const void* B, const void* C, int64_t M, int64_t N, int64_t K,
+             int64_t lda, int64_t ldb, int64_t ldc, int c_col_major) {
+  if (M < 0 || N < 0 || K < 0) return NEOGEMM_ERR_BAD_ARG;
+  if (M == 0 || N == 0) return NEOGEMM_OK;
+  if (C == nullptr) return NEOGEMM_ERR_BAD_ARG;
+  if (ldc < (c_col_major ? M : N)) return NEOGEMM_ERR_BAD_ARG;
+  if (K == 0) return NEOGEMM_OK;
+  if (A == nullptr || B == nullptr) return NEOGEMM_ERR_BAD_ARG;
+  if (lda < K || ldb < K) return NEOGEMM_ERR_BAD_ARG;
+  if (K % 8 != 0 || lda % 8 != 0 || ldb % 8 != 0) return NEOGEMM_ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) != 0 || (reinterpret_cast<uintptr_t>(B) & 15) != 0)
+    return NEOGEMM_ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(C) & 1) != 0) return NEOGEMM_ERR_UNSUPPORTED;
+  if (M > 0x7fffffffll || N > 0x7fffffffll || K > 0x7fffffffll) return NEOGEMM_ERR_UNSUPPORTED;
+  return NEOGEMM_OK;
+}
+
+int ensure_workspace(DeviceState* st, size_t bytes) {
+  if (bytes <= st->workspace_bytes) return NEOGEMM_OK;
+  if (st->workspace != nullptr) cudaFree(st->workspace);
+  st->workspace = nullptr;
+  st->workspace_bytes = 0;
+  const size_t want = std::max(bytes, static_cast<size_t>(64) << 20);
+  if (cudaMalloc(&st->workspace, want) != cudaSuccess ||
+      cudaMemset(st->workspace, 0, want) != cudaSuccess) {
+    cudaGetLastError();
+    st->workspace = nullptr;
+    return NEOGEMM_ERR_WORKSPACE;
+  }
+  st->workspace_bytes = want;
+  return NEOGEMM_OK;
+}
+
+int launch(DeviceState* st, const Plan& plan, const CUtensorMap& mx, const CUtensorMap& my,
+           const CUtensorMap& md, const GemmParams& params, cudaStream_t stream) {
+  const KernelEntry* k = plan.kernel;
+  if (!st->attr_done[plan.kernel_index]) {
+    if (cudaFuncSetAttribute(k->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, k->smem_bytes) !=
+        cudaSuccess) {
+      cudaGetLastError();
+      return NEOGEMM_ERR_LAUNCH;
+    }
+    st->attr_done[plan.kernel_index] = true;
+  }
+  cudaLaunchConfig_t cfg;
+  std::memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(static_cast<unsigned>(plan.num_ctas), 1, 1);
+  cfg.blockDim = dim3(192, 1, 1);
+  cfg.dynamicSmemBytes = static_cast<size_t>(k->smem_bytes);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  int nattr = 0;
+  if (k->cta_group == 2) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    nattr = 1;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = nattr;
+  void* args[4] = {const_cast<CUtensorMap*>(&mx), const_cast<CUtensorMap*>(&my),
+                   const_cast<CUtensorMap*>(&md), const_cast<GemmParams*>(&params)};
+  if (cudaLaunchKernelExC(&cfg, k->fn, args) != cudaSuccess) {
+    cudaGetLastError();
+    return NEOGEMM_ERR_LAUNCH;
+  }
+  return NEOGEMM_OK;
+}
+
+int gemm_device(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                int64_t lda, int64_t ldb, int64_t ldc, int c_col_major, void* workspace,
+                size_t workspace_bytes, cudaStream_t stream) {
+  int rc = validate(A, B, C, M, N, K, lda, ldb, ldc, c_col_major);
+  if (rc != NEOGEMM_OK) return rc;
+  if (M == 0 || N == 0) return NEOGEMM_OK;
+
+  DeviceState* st;
+  {
+    std::lock_guard<std::mutex> lock(g_mu);
+    st = device_state(&rc);
+  }
+  if (st == nullptr) return rc;
+  if (st->status_host[0] != 0) return NEOGEMM_ERR_DEVICE_TIMEOUT;
+
+  const int64_t pm = c_col_major ? N : M;
+  const int64_t pn = c_col_major ? M : N;
+  if (K == 0) {
+    if (cudaMemset2DAsync(C, static_cast<size_t>(ldc) * 2, 0, static_cast<size_t>(pn) * 2,
+                          static_cast<size_t>(pm), stream) != cudaSuccess) {
+      cudaGetLastError();
+      return NEOGEMM_ERR_CUDA;
+    }
+    return NEOGEMM_OK;
+  }
+  const void* U = c_col_major ? B : A;   // rows of the stored matrix
+  const void* V = c_col_major ? A : B;   // columns of the stored matrix
+  const int64_t ldu = c_col_major ? ldb : lda;
+  const int64_t ldv = c_col_major ? lda : ldb;
+
+  Plan plan;
+  rc = make_plan(pm, pn, K, ldc, C, st->sm_count, t_override, &plan);
+  if (rc != NEOGEMM_OK) return rc;
+
+  const void* X = plan.swap ? V : U;
+  const void* Y = plan.swap ? U : V;
+  const int64_t ldx = plan.swap ? ldv : ldu;
+  const int64_t ldy = plan.swap ? ldu : ldv;
+
+  CUtensorMap mx, my, md;
+  std::memset(&md, 0, sizeof(md));
+  rc = get_tensor_map(X, static_cast<uint64_t>(K), static_cast<uint64_t>(plan.Md),
+                      static_cast<uint64_t>(ldx) * 2, 128, 0, &mx);
+  if (rc != NEOGEMM_OK) return rc;
+  rc = get_tensor_map(Y, static_cast<uint64_t>(K), static_cast<uint64_t>(plan.Nd),
+                      static_cast<uint64_t>(ldy) * 2,
+                      static_cast<uint32_t>(plan.block_n / plan.cta_group), 0, &my);
+  if (rc != NEOGEMM_OK) return rc;
+  if (plan.epi == kEpiTmaStore) {
+    rc = get_tensor_map(C, static_cast<uint64_t>(plan.Nd), static_cast<uint64_t>(plan.Md),
+                        static_cast<uint64_t>(ldc) * 2, 32, 1, &md);
+    if (rc != NEOGEMM_OK) return rc;
+  }
+
+  GemmParams params;
+  std::memset(&params, 0, sizeof(params));
+  params.Md = plan.Md;
+  params.Nd = plan.Nd;
+  params.K = static_cast<int>(K);
+  params.num_m_tiles = plan.num_m_tiles;
+  params.num_n_tiles = plan.num_n_tiles;
+  params.num_tiles = plan.num_tiles;
+  params.num_k_blocks = plan.num_k_blocks;
+  params.group_m = plan.group_m;
+  params.out = static_cast<__nv_bfloat16*>(C);
+  params.out_stride_r = plan.swap ? 1 : ldc;
+  params.out_stride_c = plan.swap ? ldc : 1;
+  params.stream_k = plan.stream_k ? 1 : 0;
+  params.max_contrib = plan.max_contrib;
+  params.status = st->status_dev;
+
+  if (plan.stream_k) {
+    const size_t need = plan.counters_bytes + plan.partials_bytes;
+    char* ws = static_cast<char*>(workspace);
+    if (ws != nullptr) {
+      if (workspace_bytes < need || (reinterpret_cast<uintptr_t>(ws) & 255) != 0)
+        return NEOGEMM_ERR_WORKSPACE;
+    } else {
+      std::lock_guard<std::mutex> lock(g_mu);
+      rc = ensure_workspace(st, need);
+      if (rc != NEOGEMM_OK) return rc;
+      ws = static_cast<char*>(st->workspace);
+    }
+    params.tile_counters = reinterpret_cast<int*>(ws);
+    params.partials = reinterpret_cast<float*>(ws + plan.counters_bytes);
+  }
+
+  t_last_config[0] = plan.cta_group;
+  t_last_config[1] = plan.block_n;
+  t_last_config[2] = plan.kernel->stages;
+  t_last_config[3] = plan.swap ? 1 : 0;
+  t_last_config[4] = plan.stream_k ? 1 : 0;
+  t_last_config[5] = plan.num_ctas;
+  t_last_config[6] = plan.num_tiles;
+  t_last_config[7] = plan.group_m;
+
+  std::lock_guard<std::mutex> lock(g_mu);  // attr_done bookkeeping
+  return launch(st, plan, mx, my, md, params, stream);
+}
+
+int ensure_stage(DeviceState* st, int which, size_t bytes) {
+  if (bytes <= st->stage_bytes[which]) return NEOGEMM_OK;
+  if (st->stage[which] != nullptr) cudaFree(st->stage[which]);
+  st->stage[which] = nullptr;
+  st->stage_bytes[which] = 0;
+  if (cudaMalloc(&st->stage[which], bytes) != cudaSuccess) {
+    cudaGetLastError();
+    return NEOGEMM_ERR_CUDA;
+  }
+  st->stage_bytes[which] = bytes;
+  return NEOGEMM_OK;
+}
+
+}  // namespace
+}  // namespace neogemm
+
+using namespace neogemm;
+
+extern "C" {
+
+int neogemm_bf16_nt(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                    int64_t lda, int64_t ldb, int64_t ldc, int c_col_major, void* workspace,
+                    size_t workspace_bytes, void* stream) {
+  return gemm_device(A, B, C, M, N, K, lda, ldb, ldc, c_col_major, workspace, workspace_bytes,
+                     static_cast<cudaStream_t>(stream));
+}
+
+size_t neogemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int c_col_major) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  int rc;
+  int sm_count;
+  {
+    std::lock_guard<std::mutex> lock(g_mu);
+    DeviceState* st = device_state(&rc);
+    if (st == nullptr) return 0;
+    sm_count = st->sm_count;
+  }
+  Plan plan;
+  const int64_t pm = c_col_major ? N : M;
+  const int64_t pn = c_col_major ? M : N;
+  // Unaligned C / pitch only ever selects the direct epilogue, whose needs are the larger.
+  if (make_plan(pm, pn, K, 1, reinterpret_cast<const void*>(2), sm_count, t_override, &plan) !=
+      NEOGEMM_OK)
+    return 0;
+  const size_t direct = plan.stream_k ? plan.counters_bytes + plan.partials_bytes : 0;
+  if (make_plan(pm, pn, K, 8, nullptr, sm_count, t_override, &plan) != NEOGEMM_OK) return direct;
+  const size_t aligned = plan.stream_k ? plan.counters_bytes + plan.partials_bytes : 0;
+  return std::max(direct, aligned);
+}
+
+int neogemm_bf16_nt_host(const void* A_host, const void* B_host, void* C_host, int64_t M,
+                         int64_t N, int64_t K, int c_col_major, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (M < 0 || N < 0 || K < 0) return NEOGEMM_ERR_BAD_ARG;
+  if (M == 0 || N == 0) return NEOGEMM_OK;
+  if (C_host == nullptr || (K > 0 && (A_host == nullptr || B_host == nullptr)))
+    return NEOGEMM_ERR_BAD_ARG;
+  int rc;
+  DeviceState* st;
+  const size_t bytes_a = static_cast<size_t>(M) * K * 2, bytes_b = static_cast<size_t>(N) * K * 2,
+               bytes_c = static_cast<size_t>(M) * N * 2;
+  {
+    std::lock_guard<std::mutex> lock(g_mu);
+    st = device_state(&rc);
+    if (st == nullptr) return rc;
+    if ((rc = ensure_stage(st, 0, std::max<size_t>(bytes_a, 16))) != NEOGEMM_OK) return rc;
+    if ((rc = ensure_stage(st, 1, std::max<size_t>(bytes_b, 16))) != NEOGEMM_OK) return rc;
+    if ((rc = ensure_stage(st, 2, bytes_c)) != NEOGEMM_OK) return rc;
+  }
+  if (K > 0) {
+    if (cudaMemcpyAsync(st->stage[0], A_host, bytes_a, cudaMemcpyHostToDevice, stream) !=
+            cudaSuccess ||
+        cudaMemcpyAsync(st->stage[1], B_host, bytes_b, cudaMemcpyHostToDevice, stream) !=
+            cudaSuccess) {
+      cudaGetLastError();
+      return NEOGEMM_ERR_CUDA;
+    }
+  }
+  rc = gemm_device(st->stage[0], st->stage[1], st->stage[2], M, N, K, K, K, c_col_major ? M : N,
+                   c_col_major, nullptr, 0, stream);
+  if (rc != NEOGEMM_OK) return rc;
+  if (cudaMemcpyAsync(C_host, st->stage[2], bytes_c, cudaMemcpyDeviceToHost, stream) !=
+          cudaSuccess ||
+      cudaStreamSynchronize(stream) != cudaSuccess) {
+    cudaGetLastError();
+    return NEOGEMM_ERR_CUDA;
+  }
+  if (st->status_host[0] != 0) return NEOGEMM_ERR_DEVICE_TIMEOUT;
+  return NEOGEMM_OK;
+}
+
+int neogemm_device_status(int out[4]) {
+  if (out == nullptr) return NEOGEMM_ERR_BAD_ARG;
+  int rc;
+  std::lock_guard<std::mutex> lock(g_mu);
+  DeviceState* st = device_state(&rc);
+  if (st == nullptr) return rc;
+  for (int i = 0; i < 4; ++i) out[i] = st->status_host[i];
+  return NEOGEMM_OK;
+}
+
+int neogemm_clear_device_status(void) {
+  int rc;
+  std::lock_guard<std::mutex> lock(g_mu);
+  DeviceState* st = device_state(&rc);
+  if (st == nullptr) return rc;
+  if (cudaDeviceSynchronize() != cudaSuccess) {
+    cudaGetLastError();
+    return NEOGEMM_ERR_CUDA;
+  }
+  std::memset(st->status_host, 0, 64);
+  // A launch that gave up may have left stream-K arrival counters non-zero.
+  if (st->workspace != nullptr &&
+      cudaMemset(st->workspace, 0, st->workspace_bytes) != cudaSuccess) {
+    cudaGetLastError();
+    return NEOGEMM_ERR_CUDA;
+  }
+  return NEOGEMM_OK;
+}
+
+const char* neogemm_status_str(int status) {
+  switch (status) {
+    case NEOGEMM_OK: return "ok";
+    case NEOGEMM_ERR_BAD_ARG: return "bad argument (null pointer, negative size or short leading dimension)";
+    case NEOGEMM_ERR_UNSUPPORTED: return "unsupported (K, lda, ldb must be multiples of 8; A, B 16-byte aligned; device must be sm_100)";
+    case NEOGEMM_ERR_DESCRIPTOR: return "tensor-map encode failed or CUDA driver entry point unavailable";
+    case NEOGEMM_ERR_LAUNCH: return "kernel launch failed";
+    case NEOGEMM_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait expired in an earlier launch (see neogemm_device_status)";
+    case NEOGEMM_ERR_WORKSPACE: return "workspace too small, misaligned or could not be allocated";
+    case NEOGEMM_ERR_CUDA: return "CUDA runtime error";
+    default: return "unknown status";
+  }
+}
+
+int neogemm_last_config(int out[8]) {
+  if (out == nullptr) return NEOGEMM_ERR_BAD_ARG;
+  for (int i = 0; i < 8; ++i) out[i] = t_last_config[i];
+  return NEOGEMM_OK;
+}
+
+int neogemm_set_override(int cta_group, int block_n, int swap, int stream_k, int group_m,
+                         int max_ctas) {
+  if (cta_group > 2 || cta_group == 0) return NEOGEMM_ERR_BAD_ARG;
+  if (block_n > 0 && block_n != 16 && block_n != 32 && block_n != 64 && block_n != 128 &&
+      block_n != 256)
+    return NEOGEMM_ERR_BAD_ARG;
+  t_override.cta_group = cta_group;
+  t_override.block_n = block_n;
+  t_override.swap = swap;
+  t_override.stream_k = stream_k;
+  t_override.group_m = group_m;
+  t_override.max_ctas = max_ctas;
+  return NEOGEMM_OK;
+}
+
+int neogemm_version(void) { return 100; }
+
+}  // extern "C"

@@ -1,0 +1,117 @@
+/* neogemm.h - C ABI of the B200 (sm_100a) BF16 GEMM library, libneogemm.so.
+ *
+ * One operation:  C = A * B^T  with bf16 A[M,K] (row-major), bf16 B[N,K] (row-major, i.e. K-major),
+ * fp32 accumulation and a bf16 (round-to-nearest-even) result.  This is the operation of the
+ * reference's PyTorch-extension function neoGemmV1(A, B, C) (nemgemmV03.cu:343-391; older name
+ * neogemm(), neogemmV02.cu:262-303), driven by benchmark.py:24.
+ *
+ * Plain pointers and sizes only: no torch or C++ types cross this boundary.  All device pointers
+ * must belong to the CUDA device that is current on the calling thread.  Calls are asynchronous
+ * with respect to the host unless stated otherwise; `stream` is a cudaStream_t passed as void*
+ * (NULL = the legacy default stream, which is what the reference launches on,
+ * nemgemmV03.cu:383).
+ *
+ * There is no CPU fallback.  Every function that needs a GPU fails with an error code when no
+ * usable sm_100 device is current.
+ */
+#ifndef NEOGEMM_H_
+#define NEOGEMM_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Return codes.  0 is success; everything else leaves C unspecified. */
+enum neogemm_status {
+  NEOGEMM_OK = 0,
+  NEOGEMM_ERR_BAD_ARG = 1,        /* null pointer, negative size, bad leading dimension */
+  NEOGEMM_ERR_UNSUPPORTED = 2,    /* K % 8 != 0, lda/ldb % 8 != 0, misaligned A/B, or not sm_100 */
+  NEOGEMM_ERR_DESCRIPTOR = 3,     /* cuTensorMapEncodeTiled failed or is unavailable */
+  NEOGEMM_ERR_LAUNCH = 4,         /* cudaLaunchKernelEx / attribute set-up failed */
+  NEOGEMM_ERR_DEVICE_TIMEOUT = 5, /* an earlier launch on this device reported a bounded wait that
+                                     expired; see neogemm_device_status() */
+  NEOGEMM_ERR_WORKSPACE = 6,      /* caller's workspace too small, or internal allocation failed */
+  NEOGEMM_ERR_CUDA = 7            /* any other CUDA runtime error (copy, allocation, sync) */
+};
+
+/* C = A * B^T on device memory.
+ *
+ * Replaces the body of neoGemmV1 (nemgemmV03.cu:343-391): that function reads M = A.size(0),
+ * K = A.size(1), N = B.size(0) (:344-346), builds two tensor maps and launches one 64x64 tile per
+ * CTA.  Here the same three sizes arrive explicitly, with leading dimensions in ELEMENTS.
+ *
+ *   A   [M,K] bf16, element (i,k) at A[i*lda + k]          lda >= K, lda % 8 == 0, 16-B aligned
+ *   B   [N,K] bf16, element (j,k) at B[j*ldb + k]          ldb >= K, ldb % 8 == 0, 16-B aligned
+ *   C   bf16 result.
+ *       c_col_major == 0: element (i,j) at C[i*ldc + j], ldc >= N   (row-major [M,N])
+ *       c_col_major != 0: element (i,j) at C[j*ldc + i], ldc >= M   (column-major, which is what
+ *                         the reference writes, neogemmV02.cu:236,242, and why benchmark.py:25
+ *                         transposes the view afterwards)
+ *   M, N >= 0 (0 is a no-op), K >= 0 with K % 8 == 0 (K == 0 writes zeros).
+ *       The reference requires multiples of 64 in all three (nemgemmV03.cu:375); edges are
+ *       handled here by TMA zero-fill and clipped stores.
+ *   workspace / workspace_bytes: scratch for the stream-K schedule used on skinny shapes
+ *       (neogemm_workspace_bytes() says how much).  NULL selects a library-owned per-device
+ *       buffer that is allocated on first use; that buffer is shared by all calls on the device,
+ *       so concurrent launches on different streams must pass their own workspaces.  A caller's
+ *       workspace must be zero-filled once before its first use; the kernel leaves it reusable.
+ *   stream: cudaStream_t.
+ */
+int neogemm_bf16_nt(const void* A, const void* B, void* C,
+                    int64_t M, int64_t N, int64_t K,
+                    int64_t lda, int64_t ldb, int64_t ldc,
+                    int c_col_major,
+                    void* workspace, size_t workspace_bytes,
+                    void* stream);
+
+/* Upper bound on the workspace neogemm_bf16_nt() may need for this shape on the current device
+ * (0 when the data-parallel schedule would be chosen).  No counterpart in the reference, which
+ * has no split-K. */
+size_t neogemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int c_col_major);
+
+/* Same product with HOST buffers: copies A and B to the device, runs the kernel and copies C
+ * back, all on `stream`, then synchronises the stream.  Packed layouts (lda = ldb = K; ldc = N, or
+ * M when c_col_major).  Device staging buffers are owned by the library and reused across calls.
+ * This is the call a host program without device memory of its own makes; the reference's
+ * counterpart is the cublass/matmul.cu flow (host malloc -> cudaMemcpy -> kernel -> cudaMemcpy,
+ * matmul.cu:95-120,146-149). */
+int neogemm_bf16_nt_host(const void* A_host, const void* B_host, void* C_host,
+                         int64_t M, int64_t N, int64_t K,
+                         int c_col_major, void* stream);
+
+/* Device-side error record of the current device: out[0] = code (0 none; 1 producer wait expired,
+ * 2 MMA operand wait, 3 MMA accumulator wait, 4 epilogue wait, 5 tensor-memory address),
+ * out[1] = CTA index, out[2] = segment index, out[3] = ring stage or accumulator.  Meaningful once
+ * the stream of the launch has been synchronised.  The reference only prints cudaGetLastError
+ * (nemgemmV03.cu:387-390). */
+int neogemm_device_status(int out[4]);
+
+/* Clears the device-side error record of the current device. */
+int neogemm_clear_device_status(void);
+
+/* Human-readable text for a return code. */
+const char* neogemm_status_str(int status);
+
+/* Kernel configuration chosen by the most recent neogemm_bf16_nt() on this thread:
+ * out[0] = CTAs per tile (1 or 2), out[1] = tile columns (UMMA N), out[2] = ring stages,
+ * out[3] = 1 if operands were swapped (B rows on the 128-lane axis), out[4] = 1 if stream-K,
+ * out[5] = CTAs launched, out[6] = tiles, out[7] = raster group height. */
+int neogemm_last_config(int out[8]);
+
+/* Tuning / test override for the calling thread; -1 leaves a field to the heuristic.
+ *   cta_group: 1 or 2;  block_n: 16,32,64,128,256;  swap: 0/1;  stream_k: 0/1;
+ *   group_m: raster group height in tiles;  max_ctas: cap on launched CTAs. */
+int neogemm_set_override(int cta_group, int block_n, int swap, int stream_k, int group_m,
+                         int max_ctas);
+
+/* Library version, e.g. 100 = 1.0.0. */
+int neogemm_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* NEOGEMM_H_ */
