@@ -1,0 +1,222 @@
+"""GPU parity tests proper: the CUDA path through the C ABI against the CPU oracle.
+
+Tolerances (oracle.assert_parity): allclose rtol=1e-2/atol=1e-2 vs the fp32-accumulated product,
+relative Frobenius error <= 3e-3, >= 98 % of elements bit-equal to the RNE-rounded oracle, none
+more than 1 bf16 ulp away.
+"""
+import numpy as np
+import pytest
+import torch
+
+from gemm_b200 import ops
+from gemm_b200.inputs import make_problem
+from oracle import oracle
+from tests.util import run_case
+
+pytestmark = pytest.mark.gpu
+
+
+# ---- the benchmark configurations ------------------------------------------------------------
+def test_config_512_cube_row_and_column_major():
+    run_case(512, 512, 512)
+    run_case(512, 512, 512, col_major=True)
+
+
+def test_config_4096_cube():
+    run_case(4096, 4096, 4096)
+
+
+def test_config_8192_cube():
+    run_case(8192, 8192, 8192)
+
+
+@pytest.mark.parametrize("M", [16, 64, 128])
+def test_config_decode_shapes(M):
+    stats, cfg = run_case(M, 28672, 8192)
+    assert cfg["swap"] == 1 and cfg["stream_k"] == 1, cfg
+    run_case(M, 28672, 8192, col_major=True)
+
+
+# ---- edges the reference cannot handle (it needs multiples of 64, nemgemmV03.cu:375) ----------
+SMALL = [1, 8, 17, 64, 100, 128, 129, 200, 256, 300]
+
+
+@pytest.mark.parametrize("K", [8, 64, 72, 200, 512])
+def test_ragged_shape_sweep(K):
+    rng = np.random.default_rng(K)
+    pairs = [(m, n) for m in SMALL for n in SMALL]
+    picks = rng.choice(len(pairs), size=14, replace=False)
+    for i in picks:
+        m, n = pairs[i]
+        run_case(m, n, K, seed=1000 + int(i))
+        run_case(m, n, K, seed=2000 + int(i), col_major=True)
+
+
+@pytest.mark.parametrize("block_n,stream_k", [(256, 0), (128, 0), (128, 1), (64, 0), (64, 1),
+                                              (32, 0), (32, 1), (16, 0), (16, 1)])
+@pytest.mark.parametrize("swap", [0, 1])
+def test_every_single_cta_kernel(block_n, stream_k, swap):
+    # 520 x 776 x 1352: ragged in every dimension, several tiles, K not a multiple of 64.
+    ov = dict(cta_group=1, block_n=block_n, swap=swap, stream_k=stream_k)
+    stats, cfg = run_case(520, 776, 1352, override=ov)
+    assert cfg["block_n"] == block_n and cfg["swap"] == swap
+    run_case(520, 776, 1352, override=ov, col_major=True)
+
+
+def test_tma_store_kernels_on_aligned_output():
+    for bn in (256, 128):
+        stats, cfg = run_case(640, 1024, 704, override=dict(cta_group=1, block_n=bn, swap=0))
+        assert cfg["block_n"] == bn and cfg["stages"] in (4, 6)
+
+
+def test_stream_k_with_few_ctas_has_many_contributors():
+    # 3 tiles of 128 rows, 64 k-blocks, 7 CTAs -> ranges cut tiles in several places.
+    for ctas in (2, 5, 7, 148):
+        ov = dict(cta_group=1, block_n=32, swap=1, stream_k=1, max_ctas=ctas)
+        run_case(24, 384, 4096, override=ov)
+
+
+def test_raster_group_heights():
+    for g in (1, 3, 8, 64):
+        run_case(1408, 1280, 256, override=dict(group_m=g))
+
+
+def test_unscaled_operands_like_the_reference_driver():
+    # benchmark.py:10-11: N(0,1) operands at 1024^3, outputs of magnitude ~32.
+    run_case(1024, 1024, 1024, scale_by_k=False, col_major=True)
+
+
+def test_padded_leading_dimensions():
+    M, N, K = 300, 264, 328
+    A, B = make_problem(M, N, K, seed=77)
+    big_a = torch.zeros(M, K + 40, dtype=torch.bfloat16, device="cuda")
+    big_b = torch.zeros(N, K + 8, dtype=torch.bfloat16, device="cuda")
+    big_a[:, :K] = A.cuda()
+    big_b[:, :K] = B.cuda()
+    big_a[:, K:] = 7.0  # must never be read
+    big_b[:, K:] = -9.0
+    big_c = torch.full((M, N + 24), float("nan"), dtype=torch.bfloat16, device="cuda")
+    out = ops.matmul(big_a[:, :K], big_b[:, :K], out=big_c[:, :N])
+    torch.cuda.synchronize()
+    oracle.assert_parity(out, oracle.gemm_fp32(A, B), "padded lda/ldb/ldc")
+    assert torch.isnan(big_c[:, N:]).all(), "columns beyond N were written"
+
+
+def test_unaligned_row_pitch_of_c_uses_direct_stores():
+    M, N, K = 257, 250, 128   # ldc = 250: not a multiple of 8 -> no TMA store
+    stats, cfg = run_case(M, N, K)
+    run_case(M, N, K, col_major=True)
+
+
+def test_guard_bands_around_c_stay_untouched():
+    M, N, K = 200, 328, 192
+    A, B = make_problem(M, N, K, seed=5)
+    pad = 4096
+    flat = torch.full((pad + M * N + pad,), float("nan"), dtype=torch.bfloat16, device="cuda")
+    flat[:pad] = 123.0
+    flat[pad + M * N:] = 321.0
+    C = flat[pad:pad + M * N].view(M, N)
+    ops.matmul(A.cuda(), B.cuda(), out=C)
+    torch.cuda.synchronize()
+    assert (flat[:pad] == 123.0).all() and (flat[pad + M * N:] == 321.0).all()
+    oracle.assert_parity(C, oracle.gemm_fp32(A, B), "guard bands")
+
+
+def test_repeated_launches_are_bit_identical():
+    for (M, N, K) in [(1024, 1536, 2048), (64, 28672, 8192)]:
+        A, B = make_problem(M, N, K, seed=8)
+        dA, dB = A.cuda(), B.cuda()
+        first = ops.matmul(dA, dB).clone()
+        for _ in range(10):
+            again = ops.matmul(dA, dB)
+            assert torch.equal(first.view(torch.int16), again.view(torch.int16))
+    torch.cuda.synchronize()
+    assert ops.device_status()[0] == 0
+
+
+def test_k_zero_writes_zeros_and_empty_is_a_noop():
+    A = torch.zeros(8, 0, dtype=torch.bfloat16, device="cuda")
+    B = torch.zeros(16, 0, dtype=torch.bfloat16, device="cuda")
+    out = torch.full((8, 16), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.matmul(A, B, out=out)
+    torch.cuda.synchronize()
+    assert (out == 0).all()
+    ops.matmul(torch.zeros(0, 64, dtype=torch.bfloat16, device="cuda"),
+               torch.zeros(16, 64, dtype=torch.bfloat16, device="cuda"))
+
+
+def test_unsupported_k_raises():
+    A = torch.zeros(8, 12, dtype=torch.bfloat16, device="cuda")
+    B = torch.zeros(8, 12, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ops.NeoGemmError) as e:
+        ops.matmul(A, B)
+    assert e.value.code == 2
+
+
+def test_host_entry_point_round_trip():
+    M, N, K = 384, 520, 256
+    A, B = make_problem(M, N, K, seed=21)
+    C = torch.empty(M, N, dtype=torch.bfloat16).pin_memory()
+    ops.matmul_host(A.pin_memory(), B.pin_memory(), C)
+    oracle.assert_parity(C, oracle.gemm_fp32(A, B), "host entry")
+    Cc = torch.empty(N, M, dtype=torch.bfloat16)
+    ops.matmul_host(A, B, Cc, col_major=True)   # pageable memory works too
+    oracle.assert_parity(Cc.t(), oracle.gemm_fp32(A, B), "host entry column-major")
+
+
+def test_runs_on_a_side_stream():
+    A, B = make_problem(512, 768, 512, seed=31)
+    dA, dB = A.cuda(), B.cuda()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        out = ops.matmul(dA, dB)
+    s.synchronize()
+    oracle.assert_parity(out, oracle.gemm_fp32(A, B), "side stream")
+
+
+def test_linear_layout():
+    x = (torch.randn(3, 5, 256, generator=torch.Generator().manual_seed(2)) / 16).to(torch.bfloat16)
+    w = (torch.randn(136, 256, generator=torch.Generator().manual_seed(3)) / 16).to(torch.bfloat16)
+    y = ops.linear(x.cuda(), w.cuda())
+    assert y.shape == (3, 5, 136)
+    oracle.assert_parity(y.reshape(-1, 136), oracle.gemm_fp32(x.reshape(-1, 256), w), "linear")
+
+
+def test_golden_fixtures_on_the_gpu():
+    import glob, os
+    files = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "gemm_*.npz")))
+    assert files
+    for f in files:
+        z = np.load(f)
+        A = torch.from_numpy(z["A_bits"]).view(torch.bfloat16)
+        B = torch.from_numpy(z["B_bits"]).view(torch.bfloat16)
+        want = torch.from_numpy(z["C_bits"]).view(torch.bfloat16)
+        got = ops.matmul(A.cuda(), B.cuda()).cpu()
+        s = oracle.compare(got, want.float())
+        # the fixture is already rounded, so compare bf16 to bf16: at most one ulp apart
+        assert s["max_ulp"] <= 1 and s["near_zero_ok"] and s["bit_equal_frac"] >= 0.98, (f, s)
+
+
+def test_torch_extension_module_matches_reference_usage():
+    # The flow of the reference's benchmark.py:10-25 with the extension built by setup.py.
+    neoGEMM = pytest.importorskip("neoGEMM")
+    M, N, K = 1024, 1024, 1024
+    A, B = make_problem(M, N, K, seed=41, scale_by_k=False)
+    tA, tB = A.cuda(), B.cuda()
+    tC = torch.zeros(M, N, device="cuda").to(torch.bfloat16)
+    assert neoGEMM.neoGemmV1(tA, tB, tC) is None
+    tC = tC.t()
+    torch.cuda.synchronize()
+    oracle.assert_parity(tC, oracle.gemm_fp32(A, B), "neoGEMM.neoGemmV1")
+    tC2 = torch.zeros(M, N, device="cuda").to(torch.bfloat16)
+    neoGEMM.neogemm(A=tA, B=tB, C=tC2)
+    assert torch.equal(tC2.t().contiguous().view(torch.int16), tC.contiguous().view(torch.int16))
+    oracle.assert_parity(neoGEMM.matmul(tA, tB), oracle.gemm_fp32(A, B), "neoGEMM.matmul")
+    with pytest.raises(RuntimeError):
+        neoGEMM.neoGemmV1(tA.float(), tB, tC2)
+
+
+def test_device_status_is_clean_after_all_of_the_above():
+    torch.cuda.synchronize()
+    assert ops.device_status() == (0, 0, 0, 0)

@@ -1,0 +1,43 @@
+"""GPU parity for the two-CTA (cta_group::2) kernels: a cluster of two SMs shares each tile."""
+import pytest
+import torch
+
+from gemm_b200 import ops
+from tests.util import run_case
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("block_n", [256, 128])
+def test_pair_kernels_small(block_n):
+    stats, cfg = run_case(512, 512, 512, override=dict(cta_group=2, block_n=block_n, swap=0))
+    assert cfg["cta_group"] == 2 and cfg["block_n"] == block_n, cfg
+
+
+@pytest.mark.parametrize("block_n", [256, 128])
+def test_pair_kernels_ragged(block_n):
+    ov = dict(cta_group=2, block_n=block_n, swap=0)
+    run_case(520, 776, 1352, override=ov)                 # ragged everywhere
+    run_case(130, 264, 72, override=ov)                   # second CTA's rows mostly out of range
+    run_case(1000, 520, 200, override=ov, col_major=True)
+
+
+def test_pair_kernels_large():
+    for bn in (256, 128):
+        run_case(4096, 4096, 4096, override=dict(cta_group=2, block_n=bn, swap=0))
+    run_case(8192, 8192, 8192, override=dict(cta_group=2, block_n=256, swap=0))
+
+
+def test_pair_kernel_is_deterministic():
+    from gemm_b200.inputs import make_problem
+    A, B = make_problem(2048, 2048, 1024, seed=4)
+    dA, dB = A.cuda(), B.cuda()
+    ops.set_override(cta_group=2, block_n=256, swap=0)
+    try:
+        first = ops.matmul(dA, dB).clone()
+        for _ in range(10):
+            assert torch.equal(first.view(torch.int16), ops.matmul(dA, dB).view(torch.int16))
+    finally:
+        ops.set_override()
+    torch.cuda.synchronize()
+    assert ops.device_status()[0] == 0

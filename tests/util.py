@@ -1,0 +1,39 @@
+"""Shared helpers for the GPU parity tests (the checker is the CPU oracle)."""
+import torch
+
+from gemm_b200 import ops
+from gemm_b200.inputs import make_problem
+from oracle import oracle
+
+
+def run_case(M, N, K, col_major=False, seed=1234, override=None, scale_by_k=True, what=None,
+             expect=None, **gates):
+    """One parity case through the C ABI: seeded operands -> GPU kernel -> compare with oracle.
+    The output is poisoned with NaN first so unwritten elements cannot pass."""
+    A, B = make_problem(M, N, K, seed=seed, scale_by_k=scale_by_k)
+    dA, dB = A.cuda(), B.cuda()
+    try:
+        if override:
+            ops.set_override(**override)
+        if col_major:
+            C = torch.full((N, M), float("nan"), dtype=torch.bfloat16, device="cuda")
+            ops.neoGemmV1(dA, dB, C)
+            out = C.t()
+        else:
+            C = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+            ops.matmul(dA, dB, out=C)
+            out = C
+        cfg = ops.last_config()
+    finally:
+        if override:
+            ops.set_override()
+    torch.cuda.synchronize()
+    status = ops.device_status()
+    assert status[0] == 0, f"device reported {status} for {M}x{N}x{K} cfg={cfg}"
+    if expect:
+        for k, v in expect.items():
+            assert cfg[k] == v, f"expected {k}={v}, launcher chose {cfg}"
+    ref = oracle.gemm_fp32(A, B)
+    label = what or f"{M}x{N}x{K} col_major={col_major} cfg={cfg}"
+    stats = oracle.assert_parity(out, ref, label, **gates)
+    return stats, cfg
