@@ -56,6 +56,8 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-cublas", action="store_true")
+    ap.add_argument("--override", default="",
+                    help="tuning only: kernel override, e.g. cta_group=2,block_n=256,group_m=8")
     return ap.parse_args()
 
 
@@ -261,6 +263,9 @@ def run_ours(args):
     else:
         B = device_operand(N, K, args.seed, device)
     C = torch.empty((m_rank, N), dtype=torch.bfloat16, device=device)
+
+    if args.override:
+        ops.set_override(**{k: int(v) for k, v in (kv.split("=") for kv in args.override.split(","))})
 
     def step():
         ops.matmul(A, B, out=C)

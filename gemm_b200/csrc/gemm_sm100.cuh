@@ -44,6 +44,7 @@ enum DeviceError : int {
   kDevTimeoutMmaTmem = 3,    // MMA warp gave up waiting for a drained accumulator
   kDevTimeoutEpilogue = 4,   // epilogue gave up waiting for a finished accumulator
   kDevTmemAddress = 5,       // tensor-memory allocation did not start at column 0 (pair mode)
+  kDevBounds = 6,            // an index left its buffer (access skipped); aux: 1 partials, 2 counters, 3 C
 };
 
 struct GemmParams {
@@ -59,6 +60,8 @@ struct GemmParams {
   float* partials;           // [num_tiles][max_contrib][BLOCK_N][TILE_M] fp32
   int* tile_counters;        // [num_tiles][kCtaGroup][4], zero before launch; the last arriver
                              // of each entry re-zeroes it
+  // Extents for the self-checks of every global access the kernel computes itself.
+  long long partials_elems, counters_len, out_span;
   // Error reporting: status[0] = code, [1] = blockIdx, [2] = segment index, [3] = stage / acc.
   int* status;
 };
@@ -116,7 +119,7 @@ struct SegmentIter {
   long long u, u_end, total_units;
   int num_ctas;
 
-  __device__ __forceinline__ SegmentIter(const GemmParams& p, int worker, int num_workers) {
+  __host__ __device__ __forceinline__ SegmentIter(const GemmParams& p, int worker, int num_workers) {
     stream_k = p.stream_k;
     num_tiles = p.num_tiles;
     num_k_blocks = p.num_k_blocks;
@@ -128,19 +131,19 @@ struct SegmentIter {
     u_end = range_start(worker + 1);
   }
 
-  __device__ __forceinline__ long long range_start(int c) const {
+  __host__ __device__ __forceinline__ long long range_start(int c) const {
     return (total_units * c) / num_ctas;
   }
 
   // Index of the CTA whose range holds unit `x`.
-  __device__ __forceinline__ int owner_of(long long x) const {
+  __host__ __device__ __forceinline__ int owner_of(long long x) const {
     int c = static_cast<int>((x * num_ctas) / total_units);
     while (c + 1 < num_ctas && range_start(c + 1) <= x) ++c;
     while (c > 0 && range_start(c) > x) --c;
     return c;
   }
 
-  __device__ __forceinline__ bool next(Segment& s) {
+  __host__ __device__ __forceinline__ bool next(Segment& s) {
     if (!stream_k) {
       if (next_tile >= num_tiles) return false;
       s.tile = next_tile;
@@ -176,11 +179,12 @@ struct SegmentIter {
 // Grouped raster: consecutive tile ids walk down `group_m` tile rows before moving one tile
 // column to the right, so the tiles in flight at any moment share a few row panels of X and a
 // few column panels of Y in L2.  (The reference rasters row-major, neogemmV02.cu:190-191.)
-__device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& tm, int& tn) {
+__host__ __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& tm, int& tn) {
   const int group_size = p.group_m * p.num_n_tiles;
   const int group = tile / group_size;
   const int first_m = group * p.group_m;
-  const int rows = min(p.group_m, p.num_m_tiles - first_m);
+  const int left = p.num_m_tiles - first_m;
+  const int rows = p.group_m < left ? p.group_m : left;
   const int local = tile - group * group_size;
   tm = first_m + local % rows;
   tn = local / rows;
@@ -385,9 +389,21 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
           float* mine = const_cast<float*>(tile_partials) +
                         static_cast<size_t>(seg.contrib) * BLOCK_N * Cfg::TILE_M +
                         cta_rank * Cfg::BLOCK_M + row_in_cta;
+          const long long slot_end = (static_cast<long long>(seg.tile) * p.max_contrib +
+                                      seg.contrib + 1) * (static_cast<long long>(BLOCK_N) * Cfg::TILE_M);
+          const long long counter_idx =
+              (static_cast<long long>(seg.tile) * kCtaGroup + cta_rank) * 4 + quad;
+          const bool in_bounds = seg.contrib >= 0 && seg.contrib < p.max_contrib &&
+                                 seg.n_contrib <= p.max_contrib && slot_end <= p.partials_elems &&
+                                 counter_idx < p.counters_len;
+          if (!__all_sync(0xffffffffu, in_bounds)) {
+            if (lane == 0) report_error(p, abort_flag, kDevBounds, seg_idx, in_bounds ? 2 : 1);
+            break;
+          }
 #pragma unroll 1
           for (int c = 0; c < BLOCK_N; c += 16) {
             uint32_t r[16];
+            __syncwarp();
             tmem_ld_32x32b_x16(taddr + c, r);
             tmem_ld_wait();
 #pragma unroll
@@ -396,7 +412,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
           }
           __threadfence();
           __syncwarp();
-          int* counter = p.tile_counters + (seg.tile * kCtaGroup + static_cast<int>(cta_rank)) * 4 + quad;
+          int* counter = p.tile_counters + counter_idx;
           int prev = 0;
           if (lane == 0) prev = atomicAdd(counter, 1);
           prev = __shfl_sync(0xffffffffu, prev, 0);
@@ -458,6 +474,9 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
 #pragma unroll 1
         for (int c = 0; c < BLOCK_N; c += 16) {
           uint32_t r[16];
+          // tcgen05.ld / wait::ld are .sync.aligned: every lane must arrive together.  Lanes
+          // whose row is out of range skip the stores below and would otherwise run ahead.
+          __syncwarp();
           tmem_ld_32x32b_x16(taddr + c, r);
           tmem_ld_wait();
           if (tile_partials != nullptr) {
@@ -480,6 +499,12 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
           }
           const int col = col0 + c;
           if (row < p.Md && col < p.Nd) {
+            const int last_col = min(col + 15, p.Nd - 1);
+            const long long last = static_cast<long long>(row) * p.out_stride_r +
+                                   static_cast<long long>(last_col) * p.out_stride_c;
+            if (last >= p.out_span) {
+              report_error(p, abort_flag, kDevBounds, seg_idx, 3);
+            } else
             if (vec_ok && col + 16 <= p.Nd) {
               uint4 v0, v1;
               v0.x = pack_bf16x2(__uint_as_float(r[0]), __uint_as_float(r[1]));
@@ -505,6 +530,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
       }
 
       // Accumulator drained: hand it back to the MMA warp (one arrive per warp).
+      __syncwarp();
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) {

@@ -29,6 +29,8 @@ namespace neogemm {
 namespace {
 
 constexpr int kMaxDevices = 64;
+// Bytes reserved at the start of every stream-K workspace for arrival counters (16384 tiles).
+constexpr size_t kCounterRegionBytes = 256 * 1024;
 
 // ------------------------------------------------------------------------------------------
 // Kernel table
@@ -55,7 +57,6 @@ const KernelEntry* kernel_table(int* count) {
       make_entry<GemmConfig<1, 128, 6, kEpiTmaStore>>(),
       make_entry<GemmConfig<2, 256, 6, kEpiTmaStore>>(),
       make_entry<GemmConfig<2, 128, 8, kEpiTmaStore>>(),
-      make_entry<GemmConfig<1, 256, 4, kEpiDirect>>(),
       make_entry<GemmConfig<1, 128, 7, kEpiDirect>>(),
       make_entry<GemmConfig<1, 64, 9, kEpiDirect>>(),
       make_entry<GemmConfig<1, 32, 11, kEpiDirect>>(),
@@ -260,6 +261,9 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
   if (ov.cta_group > 0) cta_group = ov.cta_group;
   int epi = kEpiDirect;
   if (!swap && tma_store_ok && block_n >= 128) epi = kEpiTmaStore;
+  // The direct-store epilogue exists for 16..128 columns only: outputs whose pitch or address
+  // rules out the TMA store (N % 8 != 0 for a packed row-major C) take the 128-wide tile.
+  if (epi == kEpiDirect && block_n > 128) block_n = 128;
   if (cta_group == 2 && (epi != kEpiTmaStore || block_n < 128)) cta_group = 1;
   if (epi == kEpiTmaStore && block_n == 256 && ov.block_n < 0) {
     // Fewer, larger tiles only when there are enough of them to fill the machine.
@@ -294,13 +298,21 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
 
   int workers = workers_max;
   if (ov.max_ctas > 0) workers = std::max(1, std::min(workers, ov.max_ctas / cta_group));
+  if (stream_k &&
+      static_cast<size_t>(p.num_tiles) * cta_group * 4 * sizeof(int) > kCounterRegionBytes) {
+    if (ov.stream_k > 0) return NEOGEMM_ERR_UNSUPPORTED;
+    stream_k = false;
+    p.stream_k = false;
+  }
   if (stream_k) {
     const int64_t units = static_cast<int64_t>(p.num_tiles) * p.num_k_blocks;
     workers = static_cast<int>(std::min<int64_t>(workers, units));
     const int64_t per = units / workers;  // >= 1
     p.max_contrib = static_cast<int>((p.num_k_blocks + per - 1) / per) + 1;
-    p.counters_bytes = ((static_cast<size_t>(p.num_tiles) * cta_group * 4 * sizeof(int)) + 255) &
-                       ~static_cast<size_t>(255);
+    // The arrival counters always occupy the same fixed region at the start of a workspace, so
+    // that launches of different shapes sharing one workspace never see each other's partials
+    // where they expect zeroed counters.
+    p.counters_bytes = kCounterRegionBytes;
     p.partials_bytes = static_cast<size_t>(p.num_tiles) * p.max_contrib * block_n * tile_m *
                        sizeof(float);
   } else {
@@ -451,6 +463,8 @@ int gemm_device(const void* A, const void* B, void* C, int64_t M, int64_t N, int
   params.stream_k = plan.stream_k ? 1 : 0;
   params.max_contrib = plan.max_contrib;
   params.status = st->status_dev;
+  // One past the last element of C the product may touch, in elements from C.
+  params.out_span = (pm - 1) * ldc + pn;
 
   if (plan.stream_k) {
     const size_t need = plan.counters_bytes + plan.partials_bytes;
@@ -466,6 +480,8 @@ int gemm_device(const void* A, const void* B, void* C, int64_t M, int64_t N, int
     }
     params.tile_counters = reinterpret_cast<int*>(ws);
     params.partials = reinterpret_cast<float*>(ws + plan.counters_bytes);
+    params.counters_len = static_cast<long long>(plan.counters_bytes / sizeof(int));
+    params.partials_elems = static_cast<long long>(plan.partials_bytes / sizeof(float));
   }
 
   t_last_config[0] = plan.cta_group;
@@ -637,5 +653,46 @@ int neogemm_set_override(int cta_group, int block_n, int swap, int stream_k, int
 }
 
 int neogemm_version(void) { return 100; }
+
+int neogemm_debug_plan(int64_t M, int64_t N, int64_t K, int64_t ldc, int c_col_major, int sm_count,
+                       int* plan_out, int* segments, int max_segments) {
+  if (plan_out == nullptr || M <= 0 || N <= 0 || K <= 0 || sm_count <= 0)
+    return -NEOGEMM_ERR_BAD_ARG;
+  Plan plan;
+  const int64_t pm = c_col_major ? N : M;
+  const int64_t pn = c_col_major ? M : N;
+  const int rc = make_plan(pm, pn, K, ldc, nullptr, sm_count, t_override, &plan);
+  if (rc != NEOGEMM_OK) return -rc;
+  const int fields[16] = {plan.cta_group, plan.block_n, plan.kernel->stages, plan.swap ? 1 : 0,
+                          plan.stream_k ? 1 : 0, plan.num_ctas, plan.num_tiles, plan.group_m,
+                          plan.epi, plan.Md, plan.Nd, plan.num_m_tiles, plan.num_n_tiles,
+                          plan.num_k_blocks, plan.max_contrib, 0};
+  for (int i = 0; i < 16; ++i) plan_out[i] = fields[i];
+  GemmParams params;
+  std::memset(&params, 0, sizeof(params));
+  params.num_m_tiles = plan.num_m_tiles;
+  params.num_n_tiles = plan.num_n_tiles;
+  params.num_tiles = plan.num_tiles;
+  params.num_k_blocks = plan.num_k_blocks;
+  params.group_m = plan.group_m;
+  params.stream_k = plan.stream_k ? 1 : 0;
+  const int workers = plan.num_ctas / plan.cta_group;
+  int count = 0;
+  for (int w = 0; w < workers; ++w) {
+    SegmentIter it(params, w, workers);
+    Segment seg;
+    while (it.next(seg)) {
+      if (segments != nullptr && count < max_segments) {
+        int tm, tn;
+        tile_coords(params, seg.tile, tm, tn);
+        int* o = segments + 8 * count;
+        o[0] = w; o[1] = seg.tile; o[2] = seg.kb_begin; o[3] = seg.kb_count;
+        o[4] = seg.contrib; o[5] = seg.n_contrib; o[6] = tm; o[7] = tn;
+      }
+      ++count;
+    }
+  }
+  return count;
+}
 
 }  // extern "C"

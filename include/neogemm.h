@@ -83,7 +83,8 @@ int neogemm_bf16_nt_host(const void* A_host, const void* B_host, void* C_host,
                          int c_col_major, void* stream);
 
 /* Device-side error record of the current device: out[0] = code (0 none; 1 producer wait expired,
- * 2 MMA operand wait, 3 MMA accumulator wait, 4 epilogue wait, 5 tensor-memory address),
+ * 2 MMA operand wait, 3 MMA accumulator wait, 4 epilogue wait, 5 tensor-memory address,
+ * 6 an index failed the kernel's own bounds check and the access was skipped),
  * out[1] = CTA index, out[2] = segment index, out[3] = ring stage or accumulator.  Meaningful once
  * the stream of the launch has been synchronised.  The reference only prints cudaGetLastError
  * (nemgemmV03.cu:387-390). */
@@ -106,6 +107,19 @@ int neogemm_last_config(int out[8]);
  *   group_m: raster group height in tiles;  max_ctas: cap on launched CTAs. */
 int neogemm_set_override(int cta_group, int block_n, int swap, int stream_k, int group_m,
                          int max_ctas);
+
+/* Host-only view of the launcher's decisions, for tests and reports; needs no GPU.  Plans the
+ * product for a device with `sm_count` SMs and an output pitch `ldc` (16-byte aligned C assumed)
+ * and walks the kernel's own work iterator on the host.
+ *   plan_out[16]: CTAs per tile, tile columns, stages, swap, stream-K, CTAs, tiles, raster group,
+ *                 epilogue (0 TMA store, 1 direct), Md, Nd, tile rows, tile columns, k-blocks,
+ *                 partial slots per tile, 0.
+ *   segments: up to max_segments records of 8 ints {worker, tile, first k-block, k-blocks,
+ *                 contributor index, contributors, tile row, tile column} (may be NULL).
+ * Returns the number of segments, or minus a neogemm_status code.  No counterpart in the
+ * reference, whose schedule is one 64x64 tile per CTA (neogemmV02.cu:190-191). */
+int neogemm_debug_plan(int64_t M, int64_t N, int64_t K, int64_t ldc, int c_col_major, int sm_count,
+                       int* plan_out, int* segments, int max_segments);
 
 /* Library version, e.g. 100 = 1.0.0. */
 int neogemm_version(void);

@@ -149,6 +149,10 @@ def assert_parity(out: torch.Tensor, ref_fp32: torch.Tensor, what: str = "",
     s = compare(out, ref_fp32)
     assert s["finite"], f"{what}: non-finite values in the result"
     assert s["allclose_1e-2"], f"{what}: allclose(rtol=1e-2, atol=1e-2) failed: {s}"
+    # A handful of elements cannot average their rounding errors: one bf16 rounding alone can be
+    # off by the unit roundoff 2^-8 = 3.9e-3, so tiny outputs get that bound instead.
+    if out.numel() < 256:
+        rel_fro = max(rel_fro, 2.0 ** -8)
     assert s["rel_fro"] <= rel_fro, f"{what}: relative Frobenius error {s['rel_fro']:.3e}: {s}"
     assert s["bit_equal_frac"] >= bit_equal, f"{what}: only {s['bit_equal_frac']:.4f} bit-equal: {s}"
     assert s["max_ulp"] <= max_ulp, f"{what}: {s['max_ulp']} ulp away somewhere: {s}"

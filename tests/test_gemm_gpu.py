@@ -59,7 +59,9 @@ def test_every_single_cta_kernel(block_n, stream_k, swap):
     # 520 x 776 x 1352: ragged in every dimension, several tiles, K not a multiple of 64.
     ov = dict(cta_group=1, block_n=block_n, swap=swap, stream_k=stream_k)
     stats, cfg = run_case(520, 776, 1352, override=ov)
-    assert cfg["block_n"] == block_n and cfg["swap"] == swap
+    # 256-wide tiles exist with the TMA-store epilogue only; direct stores cap at 128 columns
+    want = block_n if (block_n < 256 or (swap == 0 and stream_k == 0)) else 128
+    assert cfg["block_n"] == want and cfg["swap"] == swap, cfg
     run_case(520, 776, 1352, override=ov, col_major=True)
 
 
