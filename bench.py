@@ -161,6 +161,8 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # torchrun pins OMP_NUM_THREADS=1 for its ranks; the CPU arm is meant to use every host core.
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
     name, (M, N, K) = workload_for(args)
     m_rank = M // args.gpus if name == "sharded" else M
     steps = max(1, min(args.steps, 20))

@@ -51,6 +51,13 @@ def _load() -> ctypes.CDLL:
     lib.neogemm_last_config.argtypes = [POINTER(c_int)]
     lib.neogemm_set_override.restype = c_int
     lib.neogemm_set_override.argtypes = [c_int] * 6
+    lib.neogemm_set_tuning.restype = c_int
+    lib.neogemm_set_tuning.argtypes = [c_int, c_int]
+    lib.neogemm_set_phase_timers.restype = c_int
+    lib.neogemm_set_phase_timers.argtypes = [c_void_p, c_size_t]
+    lib.neogemm_debug_plan.restype = c_int
+    lib.neogemm_debug_plan.argtypes = [c_int64, c_int64, c_int64, c_int64, c_int, c_int,
+                                       POINTER(c_int), POINTER(c_int), c_int]
     lib.neogemm_version.restype = c_int
     lib.neogemm_version.argtypes = []
     return lib

@@ -51,6 +51,10 @@ struct GemmParams {
   int Md, Nd, K;
   int num_m_tiles, num_n_tiles, num_tiles, num_k_blocks;
   int group_m;               // tile rows per raster group (L2 reuse)
+  int l2_hints;              // bit 0: X loads evict-last, bit 1: Y loads evict-first,
+                             // bit 2: D stores evict-first (0 = no hints)
+  int epi_wait_hint_ns;      // suspend hint of the epilogue's wait for an accumulator (0 = none)
+  int main_wait_hint_ns;     // suspend hint of the producer's and the MMA warp's ring waits
   // Direct epilogue / split partials.
   __nv_bfloat16* out;
   long long out_stride_r, out_stride_c;
@@ -62,6 +66,8 @@ struct GemmParams {
                              // of each entry re-zeroes it
   // Extents for the self-checks of every global access the kernel computes itself.
   long long partials_elems, counters_len, out_span;
+  // Optional phase timers (null in production): 8 clock64 sums per CTA, see PhaseTimer below.
+  long long* timers;
   // Error reporting: status[0] = code, [1] = blockIdx, [2] = segment index, [3] = stage / acc.
   int* status;
 };
@@ -190,6 +196,26 @@ __host__ __device__ __forceinline__ void tile_coords(const GemmParams& p, int ti
   tn = local / rows;
 }
 
+// Phase timers, the counterpart of the per-CTA load/compute/store cycle records the reference's
+// harness reserves a buffer for but never fills (cublass/matmul.cu:99-106,151-165).  Slots per CTA:
+//   0 producer: cycles waiting for a free ring slot     1 producer: whole loop
+//   2 MMA: cycles waiting for operand bytes             3 MMA: cycles waiting for a drained accumulator
+//   4 MMA: whole loop                                   5 epilogue warp 2: waiting for an accumulator
+//   6 epilogue warp 2: whole loop                       7 segments processed
+struct PhaseTimer {
+  long long* slot;
+  long long t0, sum;
+  __device__ __forceinline__ PhaseTimer(const GemmParams& p) {
+    slot = p.timers ? p.timers + static_cast<long long>(blockIdx.x) * 8 : nullptr;
+    t0 = 0;
+    sum = 0;
+  }
+  __device__ __forceinline__ void begin() { if (slot) t0 = clock64(); }
+  // Accumulates in a register; flush() writes the sum once, after the role's loop.
+  __device__ __forceinline__ void end() { if (slot) sum += clock64() - t0; }
+  __device__ __forceinline__ void flush(int i) { if (slot) slot[i] += sum; }
+};
+
 __device__ __forceinline__ void report_error(const GemmParams& p, volatile int* abort_flag,
                                              int code, int seg, int aux) {
   *abort_flag = 1;
@@ -270,63 +296,106 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
   // ---------------------------------------------------------------- roles
   if (warp == 0) {
     // ======================= TMA producer =======================
-    if (lane == 0 && *abort_flag == 0) {
+    // The whole warp walks the loop so that every loop-carried value stays warp-uniform; one
+    // elected lane issues the copies.
+    if (*abort_flag == 0) {
       SegmentIter it(p, worker, num_workers);
       Segment seg;
       uint32_t stage = 0, phase = 0;
       int seg_idx = 0;
       const uint32_t leader_full = (kCtaGroup == 2) ? mapa_u32(full_bar, 0) : full_bar;
+      // X is the operand the raster keeps across consecutive waves (a group of tile rows); Y
+      // streams past it.
+      const bool hint_x = (p.l2_hints & 1) != 0, hint_y = (p.l2_hints & 2) != 0;
+      const uint64_t pol_x = l2_policy_evict_last(), pol_y = l2_policy_evict_first();
       bool ok = true;
+      GemmParams timer_params = p;
+      if (lane != 0) timer_params.timers = nullptr;
+      PhaseTimer wait_timer(timer_params), loop_timer(timer_params);
+      loop_timer.begin();
       while (ok && it.next(seg)) {
         int tm, tn;
         tile_coords(p, seg.tile, tm, tn);
         const int row_x = tm * Cfg::TILE_M + static_cast<int>(cta_rank) * Cfg::BLOCK_M;
         const int row_y = tn * BLOCK_N + static_cast<int>(cta_rank) * Cfg::LOAD_N;
-        for (int kb = seg.kb_begin; kb < seg.kb_begin + seg.kb_count; ++kb) {
-          if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1, abort_flag)) {
-            report_error(p, abort_flag, kDevTimeoutProducer, seg_idx, static_cast<int>(stage));
+        const int kb_end = seg.kb_begin + seg.kb_count;
+        for (int kb = seg.kb_begin; kb < kb_end; ++kb) {
+          wait_timer.begin();
+          const bool got = __all_sync(0xffffffffu,
+                                      mbar_wait(empty_bar + 8 * stage, phase ^ 1, abort_flag,
+                                                static_cast<uint32_t>(p.main_wait_hint_ns)));
+          wait_timer.end();
+          if (!got) {
+            if (lane == 0)
+              report_error(p, abort_flag, kDevTimeoutProducer, seg_idx, static_cast<int>(stage));
             ok = false;
             break;
           }
           const uint32_t sx = ring + stage * Cfg::SMEM_STAGE;
           const uint32_t sy = sx + Cfg::SMEM_X;
-          if (kCtaGroup == 1) {
-            mbar_arrive_expect_tx(full_bar + 8 * stage, Cfg::SMEM_STAGE);
-            tma_load_2d(sx, &tmap_x, full_bar + 8 * stage, kb * Cfg::BLOCK_K, row_x);
-            tma_load_2d(sy, &tmap_y, full_bar + 8 * stage, kb * Cfg::BLOCK_K, row_y);
-          } else {
-            if (is_leader) mbar_arrive_expect_tx(full_bar + 8 * stage, 2 * Cfg::SMEM_STAGE);
-            tma_load_2d_pair(sx, &tmap_x, leader_full + 8 * stage, kb * Cfg::BLOCK_K, row_x);
-            tma_load_2d_pair(sy, &tmap_y, leader_full + 8 * stage, kb * Cfg::BLOCK_K, row_y);
+          if (elect_one()) {
+            const int c0 = kb * Cfg::BLOCK_K;
+            if (kCtaGroup == 1) {
+              mbar_arrive_expect_tx(full_bar + 8 * stage, Cfg::SMEM_STAGE);
+              if (hint_x) tma_load_2d_hint(sx, &tmap_x, full_bar + 8 * stage, c0, row_x, pol_x);
+              else tma_load_2d(sx, &tmap_x, full_bar + 8 * stage, c0, row_x);
+              if (hint_y) tma_load_2d_hint(sy, &tmap_y, full_bar + 8 * stage, c0, row_y, pol_y);
+              else tma_load_2d(sy, &tmap_y, full_bar + 8 * stage, c0, row_y);
+            } else {
+              if (is_leader) mbar_arrive_expect_tx(full_bar + 8 * stage, 2 * Cfg::SMEM_STAGE);
+              if (hint_x) tma_load_2d_pair_hint(sx, &tmap_x, leader_full + 8 * stage, c0, row_x, pol_x);
+              else tma_load_2d_pair(sx, &tmap_x, leader_full + 8 * stage, c0, row_x);
+              if (hint_y) tma_load_2d_pair_hint(sy, &tmap_y, leader_full + 8 * stage, c0, row_y, pol_y);
+              else tma_load_2d_pair(sy, &tmap_y, leader_full + 8 * stage, c0, row_y);
+            }
           }
+          __syncwarp();
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
         ++seg_idx;
       }
+      loop_timer.end();
+      loop_timer.flush(1);
+      wait_timer.flush(0);
     }
     __syncwarp();
   } else if (warp == 1) {
     // ======================= UMMA issuer (leader CTA only) =======================
-    if (lane == 0 && is_leader && *abort_flag == 0) {
+    // Warp-uniform loop, one elected lane issues tcgen05.mma / tcgen05.commit.
+    if (is_leader && *abort_flag == 0) {
       SegmentIter it(p, worker, num_workers);
       Segment seg;
       uint32_t stage = 0, phase = 0;
       int seg_idx = 0;
       constexpr uint32_t idesc = make_idesc_bf16(Cfg::TILE_M, BLOCK_N);
-      const uint32_t peer_empty = (kCtaGroup == 2) ? mapa_u32(empty_bar, 1) : 0u;
-      const uint32_t peer_tmem_full = (kCtaGroup == 2) ? mapa_u32(tmem_full_bar, 1) : 0u;
       bool ok = true;
+      GemmParams timer_params = p;
+      if (lane != 0) timer_params.timers = nullptr;
+      PhaseTimer wait_timer(timer_params), tmem_timer(timer_params), loop_timer(timer_params);
+      loop_timer.begin();
       while (ok && it.next(seg)) {
         const uint32_t acc = seg_idx & 1, acc_phase = (seg_idx >> 1) & 1;
-        if (!mbar_wait<kCtaGroup == 2>(tmem_empty_bar + 8 * acc, acc_phase ^ 1, abort_flag)) {
-          report_error(p, abort_flag, kDevTimeoutMmaTmem, seg_idx, static_cast<int>(acc));
+        tmem_timer.begin();
+        const bool drained = __all_sync(
+            0xffffffffu,
+            mbar_wait<kCtaGroup == 2>(tmem_empty_bar + 8 * acc, acc_phase ^ 1, abort_flag));
+        tmem_timer.end();
+        if (!drained) {
+          if (lane == 0)
+            report_error(p, abort_flag, kDevTimeoutMmaTmem, seg_idx, static_cast<int>(acc));
           break;
         }
         tcgen05_fence_after();
         const uint32_t tmem_d = tmem_base + acc * Cfg::kAccumCols;
         for (int kb = 0; kb < seg.kb_count; ++kb) {
-          if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag)) {
-            report_error(p, abort_flag, kDevTimeoutMmaFull, seg_idx, static_cast<int>(stage));
+          wait_timer.begin();
+          const bool got = __all_sync(0xffffffffu,
+                                      mbar_wait(full_bar + 8 * stage, phase, abort_flag,
+                                                static_cast<uint32_t>(p.main_wait_hint_ns)));
+          wait_timer.end();
+          if (!got) {
+            if (lane == 0)
+              report_error(p, abort_flag, kDevTimeoutMmaFull, seg_idx, static_cast<int>(stage));
             ok = false;
             break;
           }
@@ -334,21 +403,32 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
           const uint32_t sx = ring + stage * Cfg::SMEM_STAGE;
           const uint64_t desc_x = make_smem_desc_sw128(sx);
           const uint64_t desc_y = make_smem_desc_sw128(sx + Cfg::SMEM_X);
+          if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < Cfg::BLOCK_K / Cfg::UMMA_K; ++k) {
-            // +32 bytes (two 16-byte units) per 16-element K step inside the swizzle row.
-            umma_bf16<kCtaGroup>(tmem_d, desc_x + 2 * k, desc_y + 2 * k, idesc,
-                                 (kb > 0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < Cfg::BLOCK_K / Cfg::UMMA_K; ++k) {
+              // +32 bytes (two 16-byte units) per 16-element K step inside the swizzle row.
+              umma_bf16<kCtaGroup>(tmem_d, desc_x + 2 * k, desc_y + 2 * k, idesc,
+                                   (kb > 0 || k > 0) ? 1u : 0u);
+            }
+            if (kCtaGroup == 2) umma_commit_both_ctas(empty_bar + 8 * stage);
+            else umma_commit<1>(empty_bar + 8 * stage);
           }
-          umma_commit<kCtaGroup>(empty_bar + 8 * stage);
-          if (kCtaGroup == 2) umma_commit<kCtaGroup>(peer_empty + 8 * stage);
+          __syncwarp();
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
-        umma_commit<kCtaGroup>(tmem_full_bar + 8 * acc);
-        if (kCtaGroup == 2) umma_commit<kCtaGroup>(peer_tmem_full + 8 * acc);
+        if (elect_one()) {
+          if (kCtaGroup == 2) umma_commit_both_ctas(tmem_full_bar + 8 * acc);
+          else umma_commit<1>(tmem_full_bar + 8 * acc);
+        }
+        __syncwarp();
         ++seg_idx;
       }
+      loop_timer.end();
+      loop_timer.flush(4);
+      wait_timer.flush(2);
+      tmem_timer.flush(3);
+      if (loop_timer.slot) loop_timer.slot[7] += seg_idx;
     }
     __syncwarp();
   } else {
@@ -360,11 +440,22 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
     Segment seg;
     int seg_idx = 0;
     uint32_t store_count = 0;
+    const uint64_t pol_d = l2_policy_evict_first();
     bool ok = (*abort_flag == 0);
+    GemmParams timer_params = p;
+    if (warp != 2 || lane != 0) timer_params.timers = nullptr;
+    PhaseTimer wait_timer(timer_params), loop_timer(timer_params);
+    loop_timer.begin();
     while (ok && it.next(seg)) {
       const uint32_t acc = seg_idx & 1, acc_phase = (seg_idx >> 1) & 1;
-      bool got = mbar_wait(tmem_full_bar + 8 * acc, acc_phase, abort_flag);
-      got = __all_sync(0xffffffffu, got);
+      wait_timer.begin();
+      // One lane polls; the other 31 sleep at the shuffle instead of hammering the barrier.
+      int got_i = 0;
+      if (lane == 0)
+        got_i = mbar_wait(tmem_full_bar + 8 * acc, acc_phase, abort_flag,
+                          static_cast<uint32_t>(p.epi_wait_hint_ns)) ? 1 : 0;
+      const bool got = __shfl_sync(0xffffffffu, got_i, 0) != 0;
+      wait_timer.end();
       if (!got) {
         if (lane == 0) report_error(p, abort_flag, kDevTimeoutEpilogue, seg_idx, static_cast<int>(acc));
         break;
@@ -461,7 +552,10 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            if (my_row0 < p.Md && col0 + c < p.Nd) tma_store_2d(&tmap_d, buf, col0 + c, my_row0);
+            if (my_row0 < p.Md && col0 + c < p.Nd) {
+              if (p.l2_hints & 4) tma_store_2d_hint(&tmap_d, buf, col0 + c, my_row0, pol_d);
+              else tma_store_2d(&tmap_d, buf, col0 + c, my_row0);
+            }
             tma_store_commit();
           }
           ++store_count;
@@ -484,18 +578,24 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
             // does not depend on which contributor arrived last.
             const float* col_base = tile_partials + static_cast<size_t>(c) * Cfg::TILE_M +
                                     cta_rank * Cfg::BLOCK_M + row_in_cta;
+            float sum[16];
+#pragma unroll 1
+            for (int q = 0; q < seg.n_contrib; ++q) {
+              float t[16];
+              if (q == seg.contrib) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const float own = __uint_as_float(r[j]);
-              float v = 0.f;
-              for (int q = 0; q < seg.n_contrib; ++q) {
-                const float t = (q == seg.contrib)
-                    ? own
-                    : __ldcg(col_base + (static_cast<size_t>(q) * BLOCK_N + j) * Cfg::TILE_M);
-                v = (q == 0) ? t : v + t;
+                for (int j = 0; j < 16; ++j) t[j] = __uint_as_float(r[j]);
+              } else {
+                // 16 independent loads in flight per thread (one 128-byte line per warp each).
+                const float* src = col_base + static_cast<size_t>(q) * BLOCK_N * Cfg::TILE_M;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) t[j] = __ldcg(src + static_cast<size_t>(j) * Cfg::TILE_M);
               }
-              r[j] = __float_as_uint(v);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) sum[j] = (q == 0) ? t[j] : sum[j] + t[j];
             }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(sum[j]);
           }
           const int col = col0 + c;
           if (row < p.Md && col < p.Nd) {
@@ -540,6 +640,9 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
       ++seg_idx;
     }
     if (Cfg::kEpiMode == kEpiTmaStore && lane == 0) tma_store_wait_all<0>();
+    loop_timer.end();
+    loop_timer.flush(6);
+    wait_timer.flush(5);
     __syncwarp();
   }
 

@@ -31,6 +31,8 @@ namespace {
 constexpr int kMaxDevices = 64;
 // Bytes reserved at the start of every stream-K workspace for arrival counters (16384 tiles).
 constexpr size_t kCounterRegionBytes = 256 * 1024;
+// Defaults of the neogemm_set_tuning keys: L2 hint mask, epilogue wait hint (ns), ring wait hint (ns).
+constexpr int kDefaultTuning[3] = {0, 2000, 0};
 
 // ------------------------------------------------------------------------------------------
 // Kernel table
@@ -101,9 +103,12 @@ bool g_encode_looked_up = false;
 
 struct Override {
   int cta_group = -1, block_n = -1, swap = -1, stream_k = -1, group_m = -1, max_ctas = -1;
+  int tuning[3] = {-1, -1, -1};   // see neogemm_set_tuning
 };
 thread_local Override t_override;
 thread_local int t_last_config[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+thread_local long long* t_timers = nullptr;   // device buffer for phase timers, or null
+thread_local size_t t_timers_bytes = 0;
 
 // Must be called with g_mu held.  Returns the state of the current device or nullptr + code.
 DeviceState* device_state(int* code) {
@@ -265,10 +270,32 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
   // rules out the TMA store (N % 8 != 0 for a packed row-major C) take the 128-wide tile.
   if (epi == kEpiDirect && block_n > 128) block_n = 128;
   if (cta_group == 2 && (epi != kEpiTmaStore || block_n < 128)) cta_group = 1;
-  if (epi == kEpiTmaStore && block_n == 256 && ov.block_n < 0) {
-    // Fewer, larger tiles only when there are enough of them to fill the machine.
-    const int64_t tiles256 = ((md + 127) / 128) * ((nd + 255) / 256);
-    if (tiles256 < sm_count) block_n = 128;
+  if (epi == kEpiTmaStore) {
+    // Choose among the four TMA-store kernels by estimated time: waves of tiles over the
+    // workers (SMs, or SM pairs) times the work of one tile per SM, divided by the throughput
+    // each kernel reached at 8192^3 on a B200 (TFLOP/s, measured).  Overrides pin a field.
+    struct Candidate { int cta_group, block_n; double speed; };
+    const Candidate candidates[4] = {{2, 256, 1570.0}, {1, 256, 1430.0}, {1, 128, 1170.0},
+                                     {2, 128, 975.0}};
+    double best = 0.0;
+    int best_group = cta_group, best_n = block_n;
+    for (const Candidate& c : candidates) {
+      if (ov.cta_group > 0 && c.cta_group != ov.cta_group) continue;
+      if (ov.block_n > 0 && c.block_n != ov.block_n) continue;
+      if (c.block_n > block_n && ov.block_n < 0) continue;   // nd <= 128: no 256-wide tile
+      const int64_t workers = std::max(1, sm_count / c.cta_group);
+      const int64_t tm = 128 * c.cta_group;
+      const int64_t tiles = ((md + tm - 1) / tm) * ((nd + c.block_n - 1) / c.block_n);
+      const int64_t waves = (tiles + workers - 1) / workers;
+      const double cost = static_cast<double>(waves) * 128.0 * c.block_n / c.speed;
+      if (best == 0.0 || cost < best) {
+        best = cost;
+        best_group = c.cta_group;
+        best_n = c.block_n;
+      }
+    }
+    cta_group = best_group;
+    block_n = best_n;
   }
   p.block_n = block_n;
   p.cta_group = cta_group;
@@ -457,12 +484,19 @@ int gemm_device(const void* A, const void* B, void* C, int64_t M, int64_t N, int
   params.num_tiles = plan.num_tiles;
   params.num_k_blocks = plan.num_k_blocks;
   params.group_m = plan.group_m;
+  params.l2_hints = t_override.tuning[0] >= 0 ? t_override.tuning[0] : kDefaultTuning[0];
+  params.epi_wait_hint_ns = t_override.tuning[1] >= 0 ? t_override.tuning[1] : kDefaultTuning[1];
+  params.main_wait_hint_ns = t_override.tuning[2] >= 0 ? t_override.tuning[2] : kDefaultTuning[2];
   params.out = static_cast<__nv_bfloat16*>(C);
   params.out_stride_r = plan.swap ? 1 : ldc;
   params.out_stride_c = plan.swap ? ldc : 1;
   params.stream_k = plan.stream_k ? 1 : 0;
   params.max_contrib = plan.max_contrib;
   params.status = st->status_dev;
+  params.timers = nullptr;
+  if (t_timers != nullptr &&
+      t_timers_bytes >= static_cast<size_t>(plan.num_ctas) * 8 * sizeof(long long))
+    params.timers = t_timers;
   // One past the last element of C the product may touch, in elements from C.
   params.out_span = (pm - 1) * ldc + pn;
 
@@ -649,6 +683,20 @@ int neogemm_set_override(int cta_group, int block_n, int swap, int stream_k, int
   t_override.stream_k = stream_k;
   t_override.group_m = group_m;
   t_override.max_ctas = max_ctas;
+  return NEOGEMM_OK;
+}
+
+int neogemm_set_phase_timers(void* device_buffer, size_t bytes) {
+  if (device_buffer != nullptr && (reinterpret_cast<uintptr_t>(device_buffer) & 7) != 0)
+    return NEOGEMM_ERR_BAD_ARG;
+  t_timers = static_cast<long long*>(device_buffer);
+  t_timers_bytes = device_buffer ? bytes : 0;
+  return NEOGEMM_OK;
+}
+
+int neogemm_set_tuning(int key, int value) {
+  if (key < 0 || key > 2 || value > 1000000 || (key == 0 && value > 7)) return NEOGEMM_ERR_BAD_ARG;
+  t_override.tuning[key] = value;
   return NEOGEMM_OK;
 }
 

@@ -39,6 +39,20 @@ __device__ __forceinline__ uint32_t cluster_ctarank() {
   return r;
 }
 
+// True in exactly one lane of a fully converged warp.  Code under it is known to the compiler
+// to run on a single lane while the surrounding loop stays warp-uniform.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n"
+      ".reg .pred P1;\n"
+      "elect.sync _|P1, 0xffffffff;\n"
+      "selp.u32 %0, 1, 0, P1;\n"
+      "}\n"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 // Address of the same shared-memory offset in CTA `rank` of this cluster (shared::cluster window).
 __device__ __forceinline__ uint32_t mapa_u32(uint32_t cta_addr, uint32_t rank) {
   uint32_t out;
@@ -108,6 +122,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Same test, but the hardware may keep the thread suspended for up to `hint_ns` while the phase
+// is incomplete (it still wakes as soon as the phase completes).  Used for long waits so that
+// waiting warps do not burn issue slots and power.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+
 // Same, with cluster-scope acquire: used where the completing arrive came from the peer CTA.
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -131,17 +162,19 @@ constexpr uint64_t kWaitLimitNs = 2000ull * 1000ull * 1000ull;  // 2 s
 // (a word in shared memory).  The caller records the error and leaves its loop.
 template <bool kClusterScope = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
-                                          const volatile int* abort_flag) {
+                                          const volatile int* abort_flag, uint32_t hint_ns = 0) {
+  auto test = [&]() -> bool {
+    if (kClusterScope) return mbar_try_wait_cluster(bar, parity);
+    return hint_ns ? mbar_try_wait_hint(bar, parity, hint_ns) : mbar_try_wait(bar, parity);
+  };
   for (int i = 0; i < 16; ++i) {
-    if (kClusterScope ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity))
-      return true;
+    if (test()) return true;
   }
   const uint64_t t0 = globaltimer_ns();
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 32; ++i) {
-      if (kClusterScope ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity))
-        return true;
+      if (test()) return true;
     }
     if (*abort_flag != 0) return false;
     if (globaltimer_ns() - t0 > kWaitLimitNs) return false;
@@ -175,6 +208,49 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst_smem, const CUtens
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
       ".cta_group::2 [%0], [%1, {%3, %4}], [%2];"
       ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+// L2 eviction-priority policies for the hinted copy forms below.
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+
+__device__ __forceinline__ void tma_load_2d_hint(uint32_t dst_smem, const CUtensorMap* map,
+                                                 uint32_t bar, int32_t c0, int32_t c1,
+                                                 uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      ".L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+      ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1),
+        "l"(policy)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_load_2d_pair_hint(uint32_t dst_smem, const CUtensorMap* map,
+                                                      uint32_t cluster_bar, int32_t c0, int32_t c1,
+                                                      uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      ".cta_group::2.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+      ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(c0), "r"(c1),
+        "l"(policy)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_store_2d_hint(const CUtensorMap* map, uint32_t src_smem,
+                                                  int32_t c0, int32_t c1, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group.L2::cache_hint"
+      " [%0, {%2, %3}], [%1], %4;"
+      ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src_smem), "r"(c0), "r"(c1), "l"(policy)
       : "memory");
 }
 
@@ -272,8 +348,8 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint
 
 // Arrive (count 1) on `bar` once every tcgen05 operation issued so far by this thread has
 // completed.  `bar` is a shared::cluster address: this CTA's own barrier (a shared::cta address is
-// valid there) or the peer's (from mapa_u32).  One barrier per commit - to release a stage in
-// both CTAs of a pair the issuer commits twice.
+// valid there) or the peer's (from mapa_u32).  One barrier per commit; to signal both CTAs of a
+// pair at once use umma_commit_both_ctas().
 template <int kCtaGroup>
 __device__ __forceinline__ void umma_commit(uint32_t cluster_bar) {
   if constexpr (kCtaGroup == 1) {
@@ -283,6 +359,19 @@ __device__ __forceinline__ void umma_commit(uint32_t cluster_bar) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];"
                  ::"r"(cluster_bar) : "memory");
   }
+}
+
+// Pair mode: one commit that arrives (count 1) on the barrier at the same shared-memory offset in
+// BOTH CTAs of the pair (mask 0b11).  This is a signal fan-out of the tensor pipe's completion
+// event, not a data copy.  Measured here: the alternative of a second plain commit to the peer's
+// mapa address costs the issuing thread about 260 cycles per k-block and makes the pair kernel
+// issue-bound.
+__device__ __forceinline__ void umma_commit_both_ctas(uint32_t bar) {
+  const uint16_t mask = 3;
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64"
+      " [%0], %1;"
+      ::"r"(bar), "h"(mask) : "memory");
 }
 
 // TMEM -> registers: lane (base + laneid) of the warp's quadrant, 32 / 16 consecutive fp32 columns.

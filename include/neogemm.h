@@ -108,6 +108,26 @@ int neogemm_last_config(int out[8]);
 int neogemm_set_override(int cta_group, int block_n, int swap, int stream_k, int group_m,
                          int max_ctas);
 
+/* Tuning knobs of the calling thread; value -1 restores the library default.
+ *   key 0: L2 eviction hints of the TMA copies.  Bit 0: loads of the operand on the 128-lane axis
+ *          are evict-last; bit 1: loads of the other operand are evict-first; bit 2: stores of C
+ *          are evict-first.
+ *   key 1: nanoseconds the epilogue warps may stay suspended in one mbarrier.try_wait while they
+ *          wait for a finished accumulator (0 = plain try_wait).
+ *   key 2: the same for the TMA producer's and the MMA warp's waits on the operand ring.
+ * No counterpart in the reference (its maps only set L2 promotion, nemgemmV03.cu:52). */
+int neogemm_set_tuning(int key, int value);
+
+/* Profiling aid.  While a device buffer is registered on the calling thread, every launch adds
+ * clock64 sums to it, 8 int64 per CTA: [0] producer waiting for a ring slot, [1] producer loop,
+ * [2] MMA waiting for operand bytes, [3] MMA waiting for a drained accumulator, [4] MMA loop,
+ * [5] first epilogue warp waiting for an accumulator, [6] its loop, [7] segments processed.
+ * The buffer must hold 64 bytes per launched CTA and be zeroed by the caller; NULL switches the
+ * timers off (the default; the timed paths then cost one predicated branch).  This is the filled-in
+ * version of the per-CTA load/compute/store cycle records the reference's harness only reserves
+ * (cublass/matmul.cu:99-106,151-165). */
+int neogemm_set_phase_timers(void* device_buffer, size_t bytes);
+
 /* Host-only view of the launcher's decisions, for tests and reports; needs no GPU.  Plans the
  * product for a device with `sm_count` SMs and an output pitch `ldc` (16-byte aligned C assumed)
  * and walks the kernel's own work iterator on the host.
