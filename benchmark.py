@@ -1,0 +1,95 @@
+#!/usr/bin/env python
+"""Driver with the role of the reference's benchmark.py: build operands, run the extension's
+neoGemmV1(A, B, C), view the column-major result through C.t(), compare it with torch's own bf16
+matmul on the same GPU and time both (reference flow: benchmark.py:10-25 operands and call,
+:33-53 error statistics and tolerance ladder, :63-100 timing and TFLOPS = 2*M*N*K / t / 1e12).
+
+Differences from the reference script: sizes and seed come from the command line (the reference
+hard-codes 1024^3 and draws unseeded operands, benchmark.py:6-11), timing uses CUDA events on the
+launching stream instead of host wall clock around a final synchronize (benchmark.py:91-96), and
+the comparison is asserted (exit status 1 on failure) as well as printed.
+
+    python benchmark.py [--m 1024 --n 1024 --k 1024] [--seed 0] [--iters 100] [--scaled]
+"""
+import argparse
+import sys
+
+import torch
+
+import neoGEMM
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--m", type=int, default=1024)
+    ap.add_argument("--n", type=int, default=1024)
+    ap.add_argument("--k", type=int, default=1024)
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--iters", type=int, default=100)
+    ap.add_argument("--scaled", action="store_true",
+                    help="scale operands by 1/sqrt(K) (the reference uses unscaled N(0,1))")
+    return ap.parse_args()
+
+
+def time_ms(fn, iters):
+    for _ in range(10):
+        fn()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(iters):
+        fn()
+    stop.record()
+    stop.synchronize()
+    return start.elapsed_time(stop) / iters
+
+
+def main():
+    args = parse_args()
+    M, N, K = args.m, args.n, args.k
+    g = torch.Generator(device="cuda").manual_seed(args.seed)
+    scale = K ** -0.5 if args.scaled else 1.0
+    tensorA = (torch.randn(M, K, device="cuda", generator=g) * scale).to(torch.bfloat16)
+    tensorB = (torch.randn(N, K, device="cuda", generator=g) * scale).to(torch.bfloat16)
+    tensorC = torch.zeros(M, N, device="cuda").to(torch.bfloat16)
+
+    print("=== comparison ===")
+    torch_result = tensorA @ tensorB.t()
+    print(f"1. torch bf16 matmul: shape {tuple(torch_result.shape)}, dtype {torch_result.dtype}")
+    print(torch_result[:3, :3])
+
+    neoGEMM.neoGemmV1(tensorA, tensorB, tensorC)
+    result = tensorC.t()            # the kernel writes column-major, as the reference does
+    print(f"2. neoGEMM.neoGemmV1: shape {tuple(result.shape)}, dtype {result.dtype}")
+    print(result[:3, :3])
+
+    diff = (result.float() - torch_result.float()).abs()
+    print("\n=== differences ===")
+    print(f"max error : {diff.max().item():.8f}")
+    print(f"mean error: {diff.mean().item():.8f}")
+    print(f"RMS error : {diff.pow(2).mean().sqrt().item():.8f}")
+    print(f"torch   min {torch_result.min().item():.4f} max {torch_result.max().item():.4f}")
+    print(f"neoGEMM min {result.min().item():.4f} max {result.max().item():.4f}")
+
+    print("\n=== closeness ===")
+    ok = True
+    for tol in (1e-2, 1e-3, 1e-4, 1e-5):
+        close = torch.allclose(result.float(), torch_result.float(), atol=tol, rtol=tol)
+        print(f"tolerance {tol:.0e}: {'PASS' if close else 'fail'}")
+        if tol == 1e-2:
+            ok = close
+    within = (diff < 1e-3).float().mean().item() * 100
+    print(f"elements within 1e-3: {within:.2f}%")
+
+    flops = 2 * M * N * K
+    Bt = tensorB.t()
+    t_torch = time_ms(lambda: torch.matmul(tensorA, Bt), args.iters)
+    t_neo = time_ms(lambda: neoGEMM.neoGemmV1(tensorA, tensorB, tensorC), args.iters)
+    print("\n=== timing (CUDA events) ===")
+    print(f"torch  : {t_torch:.4f} ms  {flops / t_torch / 1e9:.2f} TFLOPS")
+    print(f"neoGEMM: {t_neo:.4f} ms  {flops / t_neo / 1e9:.2f} TFLOPS")
+    return 0 if ok else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -66,7 +66,7 @@ struct GemmParams {
                              // of each entry re-zeroes it
   // Extents for the self-checks of every global access the kernel computes itself.
   long long partials_elems, counters_len, out_span;
-  // Optional phase timers (null in production): 8 clock64 sums per CTA, see PhaseTimer below.
+  // Optional phase timers (null in production): 16 int64 per CTA, see PhaseTimer below.
   long long* timers;
   // Error reporting: status[0] = code, [1] = blockIdx, [2] = segment index, [3] = stage / acc.
   int* status;
@@ -89,7 +89,11 @@ struct GemmConfig {
   static constexpr int EPI_COLS = 64;                 // columns per TMA-store box (128 B of bf16)
   static constexpr int SMEM_EPI_WARP_BUF = 32 * EPI_COLS * 2;  // 4 KB: 32 rows x 128 B
   static constexpr int kEpiBufs = 2;
-  static constexpr int SMEM_EPI = (kEpiMode == kEpiTmaStore) ? 4 * kEpiBufs * SMEM_EPI_WARP_BUF : 0;
+  // Direct mode stages a warp's 32 rows x BLOCK_N columns transposed ([column][32 rows], 64 B per
+  // column) so that a transposed result leaves as 16-byte vectors instead of 2-byte scalars.
+  static constexpr int SMEM_EPI_T_WARP = BLOCK_N * 64;
+  static constexpr int SMEM_EPI = (kEpiMode == kEpiTmaStore) ? 4 * kEpiBufs * SMEM_EPI_WARP_BUF
+                                                             : 4 * SMEM_EPI_T_WARP;
   static constexpr int SMEM_BARRIERS = (2 * kStages + 4) * 8 + 16;
   // +1024: the ring must start on a 1024-byte boundary for the 128-byte swizzle.
   static constexpr int SMEM_TOTAL = kStages * SMEM_STAGE + SMEM_EPI + SMEM_BARRIERS + 1024;
@@ -121,9 +125,9 @@ struct SegmentIter {
   int stream_k, num_tiles, num_k_blocks;
   // data-parallel
   int next_tile, tile_step;
-  // stream-K
-  long long u, u_end, total_units;
-  int num_ctas;
+  // stream-K: this CTA's unit range [u0, u1) cut into head partial, tail partial, whole tiles
+  long long u0, u1, head_end, tail_begin, whole, total_units;
+  int num_ctas, phase;
 
   __host__ __device__ __forceinline__ SegmentIter(const GemmParams& p, int worker, int num_workers) {
     stream_k = p.stream_k;
@@ -133,8 +137,18 @@ struct SegmentIter {
     tile_step = num_workers;
     num_ctas = num_workers;
     total_units = static_cast<long long>(p.num_tiles) * p.num_k_blocks;
-    u = range_start(worker);
-    u_end = range_start(worker + 1);
+    phase = 0;
+    u0 = range_start(worker);
+    u1 = range_start(worker + 1);
+    const long long nk = num_k_blocks > 0 ? num_k_blocks : 1;
+    head_end = u0;
+    if (u0 % nk != 0) {
+      head_end = (u0 / nk + 1) * nk;
+      if (head_end > u1) head_end = u1;
+    }
+    tail_begin = u1;
+    if (u1 % nk != 0 && (u1 / nk) * nk >= head_end) tail_begin = (u1 / nk) * nk;
+    whole = head_end;
   }
 
   __host__ __device__ __forceinline__ long long range_start(int c) const {
@@ -149,6 +163,26 @@ struct SegmentIter {
     return c;
   }
 
+  __host__ __device__ __forceinline__ void emit(Segment& s, long long a, long long b) const {
+    const int tile = static_cast<int>(a / num_k_blocks);
+    const long long tile_u0 = static_cast<long long>(tile) * num_k_blocks;
+    s.tile = tile;
+    s.kb_begin = static_cast<int>(a - tile_u0);
+    s.kb_count = static_cast<int>(b - a);
+    if (s.kb_count == num_k_blocks) {
+      s.contrib = 0;
+      s.n_contrib = 1;
+    } else {
+      const int first = owner_of(tile_u0);
+      const int last = owner_of(tile_u0 + num_k_blocks - 1);
+      s.contrib = owner_of(a) - first;
+      s.n_contrib = last - first + 1;
+    }
+  }
+
+  // Stream-K order: the two partial segments first, whole tiles last.  A cut tile costs its
+  // contributors a round trip through the fp32 workspace; doing those early hides that work
+  // under the main loop of the following segments, and the CTA ends on a plain epilogue.
   __host__ __device__ __forceinline__ bool next(Segment& s) {
     if (!stream_k) {
       if (next_tile >= num_tiles) return false;
@@ -160,25 +194,26 @@ struct SegmentIter {
       next_tile += tile_step;
       return true;
     }
-    if (u >= u_end) return false;
-    const int tile = static_cast<int>(u / num_k_blocks);
-    const long long tile_u0 = static_cast<long long>(tile) * num_k_blocks;
-    const long long tile_u1 = tile_u0 + num_k_blocks;
-    const long long seg_end = tile_u1 < u_end ? tile_u1 : u_end;
-    s.tile = tile;
-    s.kb_begin = static_cast<int>(u - tile_u0);
-    s.kb_count = static_cast<int>(seg_end - u);
-    if (s.kb_count == num_k_blocks) {
-      s.contrib = 0;
-      s.n_contrib = 1;
-    } else {
-      const int first = owner_of(tile_u0);
-      const int last = owner_of(tile_u1 - 1);
-      s.contrib = owner_of(u) - first;
-      s.n_contrib = last - first + 1;
+    if (phase == 0) {
+      phase = 1;
+      if (head_end > u0) {
+        emit(s, u0, head_end);
+        return true;
+      }
     }
-    u = seg_end;
-    return true;
+    if (phase == 1) {
+      phase = 2;
+      if (u1 > tail_begin) {
+        emit(s, tail_begin, u1);
+        return true;
+      }
+    }
+    if (whole < tail_begin) {
+      emit(s, whole, whole + num_k_blocks);
+      whole += num_k_blocks;
+      return true;
+    }
+    return false;
   }
 };
 
@@ -202,11 +237,13 @@ __host__ __device__ __forceinline__ void tile_coords(const GemmParams& p, int ti
 //   2 MMA: cycles waiting for operand bytes             3 MMA: cycles waiting for a drained accumulator
 //   4 MMA: whole loop                                   5 epilogue warp 2: waiting for an accumulator
 //   6 epilogue warp 2: whole loop                       7 segments processed
+//   8 CTA start   9 MMA loop start   10 MMA loop end   11 epilogue loop end   12 CTA end
+//   (8..12 are %globaltimer nanoseconds, so that CTAs can be laid on one time axis)
 struct PhaseTimer {
   long long* slot;
   long long t0, sum;
   __device__ __forceinline__ PhaseTimer(const GemmParams& p) {
-    slot = p.timers ? p.timers + static_cast<long long>(blockIdx.x) * 8 : nullptr;
+    slot = p.timers ? p.timers + static_cast<long long>(blockIdx.x) * 16 : nullptr;
     t0 = 0;
     sum = 0;
   }
@@ -214,6 +251,9 @@ struct PhaseTimer {
   // Accumulates in a register; flush() writes the sum once, after the role's loop.
   __device__ __forceinline__ void end() { if (slot) sum += clock64() - t0; }
   __device__ __forceinline__ void flush(int i) { if (slot) slot[i] += sum; }
+  __device__ __forceinline__ void stamp(int i) {
+    if (slot) slot[i] = static_cast<long long>(ptx::globaltimer_ns());
+  }
 };
 
 __device__ __forceinline__ void report_error(const GemmParams& p, volatile int* abort_flag,
@@ -263,6 +303,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
 
   // ---------------------------------------------------------------- set-up
   if (threadIdx.x == 0) {
+    PhaseTimer(p).stamp(8);
     *abort_flag = 0;
     for (int s = 0; s < kStages; ++s) {
       mbar_init(full_bar + 8 * s, 1);   // one arrive.expect_tx per phase (leader's producer)
@@ -372,6 +413,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
       GemmParams timer_params = p;
       if (lane != 0) timer_params.timers = nullptr;
       PhaseTimer wait_timer(timer_params), tmem_timer(timer_params), loop_timer(timer_params);
+      loop_timer.stamp(9);
       loop_timer.begin();
       while (ok && it.next(seg)) {
         const uint32_t acc = seg_idx & 1, acc_phase = (seg_idx >> 1) & 1;
@@ -425,6 +467,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
         ++seg_idx;
       }
       loop_timer.end();
+      loop_timer.stamp(10);
       loop_timer.flush(4);
       wait_timer.flush(2);
       tmem_timer.flush(3);
@@ -515,6 +558,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
         }
       }
 
+      bool transposed = false;
       if (!finish) {
         // nothing to store: another contributor completes these rows
       } else
@@ -565,6 +609,11 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
         __nv_bfloat16* out_row = p.out + static_cast<long long>(row) * p.out_stride_r;
         const bool vec_ok = (p.out_stride_c == 1) && ((p.out_stride_r & 7) == 0) &&
                             ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+        // Transposed result (rows of D are contiguous in memory): stage, then 16-byte stores.
+        transposed = (p.out_stride_r == 1) && ((p.out_stride_c & 7) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+        const uint32_t stg = epi_base + (warp - 2) * Cfg::SMEM_EPI_T_WARP;
+        if (transposed) __syncwarp();   // the previous tile's write-out has left the staging
 #pragma unroll 1
         for (int c = 0; c < BLOCK_N; c += 16) {
           uint32_t r[16];
@@ -598,6 +647,12 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
             for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(sum[j]);
           }
           const int col = col0 + c;
+          if (transposed) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              st_shared_b16(stg + static_cast<uint32_t>(c + j) * 64u + lane * 2u,
+                            __bfloat16_as_ushort(__float2bfloat16_rn(__uint_as_float(r[j]))));
+          } else
           if (row < p.Md && col < p.Nd) {
             const int last_col = min(col + 15, p.Nd - 1);
             const long long last = static_cast<long long>(row) * p.out_stride_r +
@@ -637,10 +692,39 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
         if (kCtaGroup == 2) mbar_arrive_cluster(leader_tmem_empty + 8 * acc);
         else mbar_arrive(tmem_empty_bar + 8 * acc);
       }
+      if constexpr (Cfg::kEpiMode == kEpiDirect) {
+        if (finish && transposed) {
+          // Write-out of the staged tile: column m of D is 32 contiguous bf16 (64 B) of the
+          // result; four lanes cover one column, the warp covers eight columns per store.
+          const uint32_t stg = epi_base + (warp - 2) * Cfg::SMEM_EPI_T_WARP;
+          const int n0 = row0 + static_cast<int>(quad) * 32 + static_cast<int>(lane & 3u) * 8;
+#pragma unroll 1
+          for (int m = static_cast<int>(lane >> 2); m < BLOCK_N; m += 8) {
+            const int col = col0 + m;
+            if (col >= p.Nd || n0 >= p.Md) continue;
+            const long long off = static_cast<long long>(col) * p.out_stride_c + n0;
+            uint32_t v[4];
+            ld_shared_v4(stg + static_cast<uint32_t>(m) * 64u + (lane & 3u) * 16u, v);
+            if (n0 + 8 <= p.Md) {
+              if (off + 8 > p.out_span) {
+                report_error(p, abort_flag, kDevBounds, seg_idx, 3);
+              } else {
+                *reinterpret_cast<uint4*>(p.out + off) = make_uint4(v[0], v[1], v[2], v[3]);
+              }
+            } else {
+              const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(v);
+              for (int j = 0; j < 8 && n0 + j < p.Md; ++j) {
+                if (off + j < p.out_span) p.out[off + j] = e[j];
+              }
+            }
+          }
+        }
+      }
       ++seg_idx;
     }
     if (Cfg::kEpiMode == kEpiTmaStore && lane == 0) tma_store_wait_all<0>();
     loop_timer.end();
+    loop_timer.stamp(11);
     loop_timer.flush(6);
     wait_timer.flush(5);
     __syncwarp();
@@ -659,6 +743,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
     tcgen05_fence_after();
     tmem_dealloc<1>(tmem_base, Cfg::kTmemCols);
   }
+  if (threadIdx.x == 0) PhaseTimer(p).stamp(12);
 }
 
 }  // namespace neogemm

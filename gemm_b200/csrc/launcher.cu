@@ -59,9 +59,9 @@ const KernelEntry* kernel_table(int* count) {
       make_entry<GemmConfig<1, 128, 6, kEpiTmaStore>>(),
       make_entry<GemmConfig<2, 256, 6, kEpiTmaStore>>(),
       make_entry<GemmConfig<2, 128, 8, kEpiTmaStore>>(),
-      make_entry<GemmConfig<1, 128, 7, kEpiDirect>>(),
-      make_entry<GemmConfig<1, 64, 9, kEpiDirect>>(),
-      make_entry<GemmConfig<1, 32, 11, kEpiDirect>>(),
+      make_entry<GemmConfig<1, 128, 6, kEpiDirect>>(),
+      make_entry<GemmConfig<1, 64, 8, kEpiDirect>>(),
+      make_entry<GemmConfig<1, 32, 10, kEpiDirect>>(),
       make_entry<GemmConfig<1, 16, 12, kEpiDirect>>(),
   };
   *count = static_cast<int>(sizeof(table) / sizeof(table[0]));
@@ -495,7 +495,7 @@ int gemm_device(const void* A, const void* B, void* C, int64_t M, int64_t N, int
   params.status = st->status_dev;
   params.timers = nullptr;
   if (t_timers != nullptr &&
-      t_timers_bytes >= static_cast<size_t>(plan.num_ctas) * 8 * sizeof(long long))
+      t_timers_bytes >= static_cast<size_t>(plan.num_ctas) * 16 * sizeof(long long))
     params.timers = t_timers;
   // One past the last element of C the product may touch, in elements from C.
   params.out_span = (pm - 1) * ldc + pn;

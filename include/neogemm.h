@@ -118,11 +118,13 @@ int neogemm_set_override(int cta_group, int block_n, int swap, int stream_k, int
  * No counterpart in the reference (its maps only set L2 promotion, nemgemmV03.cu:52). */
 int neogemm_set_tuning(int key, int value);
 
-/* Profiling aid.  While a device buffer is registered on the calling thread, every launch adds
- * clock64 sums to it, 8 int64 per CTA: [0] producer waiting for a ring slot, [1] producer loop,
- * [2] MMA waiting for operand bytes, [3] MMA waiting for a drained accumulator, [4] MMA loop,
- * [5] first epilogue warp waiting for an accumulator, [6] its loop, [7] segments processed.
- * The buffer must hold 64 bytes per launched CTA and be zeroed by the caller; NULL switches the
+/* Profiling aid.  While a device buffer is registered on the calling thread, every launch records
+ * into it, 16 int64 per CTA.  Clock-cycle sums (added to what is there): [0] producer waiting for
+ * a ring slot, [1] producer loop, [2] MMA waiting for operand bytes, [3] MMA waiting for a drained
+ * accumulator, [4] MMA loop, [5] first epilogue warp waiting for an accumulator, [6] its loop,
+ * [7] segments processed.  Timestamps in %globaltimer nanoseconds (overwritten): [8] CTA start,
+ * [9] MMA loop start, [10] MMA loop end, [11] epilogue loop end, [12] CTA end.
+ * The buffer must hold 128 bytes per launched CTA and be zeroed by the caller; NULL switches the
  * timers off (the default; the timed paths then cost one predicated branch).  This is the filled-in
  * version of the per-CTA load/compute/store cycle records the reference's harness only reserves
  * (cublass/matmul.cu:99-106,151-165). */
