@@ -45,6 +45,15 @@ WORKLOADS = {
 }
 
 
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch of the dominant kernel,
+# from the ncu captures summarised under profiles/ (same bench.py command lines).
+NCU_TRAFFIC_BYTES = {
+    "8192": 1068594000 + 127370240,
+    "decode16": 472501760 + 5468416,
+    "decode128": 482692608 + 20661760,
+}
+
+
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -299,7 +308,8 @@ def run_ours(args):
     per_launch = elapsed / args.steps
     peaks = roofline.load_measured_peaks()
     sustained = elapsed > 1.0
-    roof = roofline.roofline_record(m_rank, N, K, per_launch, peaks, sustained=sustained)
+    roof = roofline.roofline_record(m_rank, N, K, per_launch, peaks, sustained=sustained,
+                                    traffic_bytes=NCU_TRAFFIC_BYTES.get(name) if world == 1 else None)
 
     # ---- cuBLAS through torch.matmul, timed the same way, for context -------------------------
     cublas = None
