@@ -59,10 +59,15 @@ struct GemmParams {
   __nv_bfloat16* out;
   long long out_stride_r, out_stride_c;
   // Stream-K (zero / null in the data-parallel schedule).
-  int stream_k;              // 1: CTA c owns units [c*U/G, (c+1)*U/G) of the (tile x k-block) space
+  int stream_k;              // 1: tiles >= sk_first_tile are cut: CTA c owns units [c*U/G, (c+1)*U/G)
+                             // of their (tile x k-block) space; tiles below go round-robin
+  int sk_first_tile;         // first tile of the stream-K region (0 = every tile)
+  int sk_splits;             // > 0: every tile of the region is cut into this many equal k-chunks,
+                             // one per worker (worker w takes chunk w / tiles of tile w % tiles),
+                             // instead of one contiguous unit range per worker
   int max_contrib;           // partial slots per tile in `partials`
-  float* partials;           // [num_tiles][max_contrib][BLOCK_N][TILE_M] fp32
-  int* tile_counters;        // [num_tiles][kCtaGroup][4], zero before launch; the last arriver
+  float* partials;           // [stream-K tiles][max_contrib][BLOCK_N][TILE_M] fp32
+  int* tile_counters;        // [stream-K tiles][kCtaGroup][4], zero before launch; the last arriver
                              // of each entry re-zeroes it
   // Extents for the self-checks of every global access the kernel computes itself.
   long long partials_elems, counters_len, out_span;
@@ -118,29 +123,35 @@ struct Segment {
   int kb_count;   // k-blocks in this segment (>= 1)
   int contrib;    // index of this segment among the tile's contributors (0 if whole)
   int n_contrib;  // contributors of this tile (1 if whole)
+  int sk_slot;    // index of the tile inside the stream-K region (workspace slot)
 };
 
 // Enumerates this CTA's segments.  Every role constructs one and walks the same sequence.
 struct SegmentIter {
-  int stream_k, num_tiles, num_k_blocks;
-  // data-parallel
-  int next_tile, tile_step;
-  // stream-K: this CTA's unit range [u0, u1) cut into head partial, tail partial, whole tiles
+  int num_k_blocks;
+  // round-robin part: tiles [0, dp_tiles)
+  int next_tile, tile_step, dp_tiles;
+  // stream-K part: tiles [sk_first, sk_first + sk_tiles); this CTA's unit range [u0, u1) is cut
+  // into head partial, tail partial and whole tiles
+  int sk_first, sk_tiles;
   long long u0, u1, head_end, tail_begin, whole, total_units;
-  int num_ctas, phase;
+  int num_ctas, phase, splits, worker_id;
 
   __host__ __device__ __forceinline__ SegmentIter(const GemmParams& p, int worker, int num_workers) {
-    stream_k = p.stream_k;
-    num_tiles = p.num_tiles;
     num_k_blocks = p.num_k_blocks;
     next_tile = worker;
     tile_step = num_workers;
     num_ctas = num_workers;
-    total_units = static_cast<long long>(p.num_tiles) * p.num_k_blocks;
-    phase = 0;
-    u0 = range_start(worker);
-    u1 = range_start(worker + 1);
+    sk_first = p.stream_k ? p.sk_first_tile : p.num_tiles;
+    sk_tiles = p.num_tiles - sk_first;
+    dp_tiles = sk_first;
+    total_units = static_cast<long long>(sk_tiles) * p.num_k_blocks;
+    phase = sk_tiles > 0 ? 0 : 3;
+    splits = p.stream_k ? p.sk_splits : 0;
+    worker_id = worker;
     const long long nk = num_k_blocks > 0 ? num_k_blocks : 1;
+    u0 = total_units > 0 ? range_start(worker) : 0;
+    u1 = total_units > 0 ? range_start(worker + 1) : 0;
     head_end = u0;
     if (u0 % nk != 0) {
       head_end = (u0 / nk + 1) * nk;
@@ -164,9 +175,10 @@ struct SegmentIter {
   }
 
   __host__ __device__ __forceinline__ void emit(Segment& s, long long a, long long b) const {
-    const int tile = static_cast<int>(a / num_k_blocks);
-    const long long tile_u0 = static_cast<long long>(tile) * num_k_blocks;
-    s.tile = tile;
+    const int slot = static_cast<int>(a / num_k_blocks);
+    const long long tile_u0 = static_cast<long long>(slot) * num_k_blocks;
+    s.tile = sk_first + slot;
+    s.sk_slot = slot;
     s.kb_begin = static_cast<int>(a - tile_u0);
     s.kb_count = static_cast<int>(b - a);
     if (s.kb_count == num_k_blocks) {
@@ -180,19 +192,28 @@ struct SegmentIter {
     }
   }
 
-  // Stream-K order: the two partial segments first, whole tiles last.  A cut tile costs its
-  // contributors a round trip through the fp32 workspace; doing those early hides that work
-  // under the main loop of the following segments, and the CTA ends on a plain epilogue.
+  // Order: the stream-K share first (its two partial segments, then its whole tiles), the
+  // round-robin tiles last.  A cut tile costs its contributors a round trip through the fp32
+  // workspace; doing that early hides it under the main loop of the following segments, and the
+  // CTA ends on a plain epilogue.
   __host__ __device__ __forceinline__ bool next(Segment& s) {
-    if (!stream_k) {
-      if (next_tile >= num_tiles) return false;
-      s.tile = next_tile;
-      s.kb_begin = 0;
-      s.kb_count = num_k_blocks;
-      s.contrib = 0;
-      s.n_contrib = 1;
-      next_tile += tile_step;
-      return true;
+    if (phase == 0 && splits > 0) {
+      // Uniform cut: all workers holding chunk i of their tiles walk the same k range at the
+      // same time, so tiles that share a row or column panel still share it in L2.
+      phase = 3;
+      const int chunk = worker_id / sk_tiles;
+      if (chunk < splits) {
+        const int slot = worker_id - chunk * sk_tiles;
+        const int kb0 = static_cast<int>(static_cast<long long>(num_k_blocks) * chunk / splits);
+        const int kb1 = static_cast<int>(static_cast<long long>(num_k_blocks) * (chunk + 1) / splits);
+        s.tile = sk_first + slot;
+        s.sk_slot = slot;
+        s.kb_begin = kb0;
+        s.kb_count = kb1 - kb0;
+        s.contrib = splits > 1 ? chunk : 0;
+        s.n_contrib = splits;
+        return true;
+      }
     }
     if (phase == 0) {
       phase = 1;
@@ -208,12 +229,23 @@ struct SegmentIter {
         return true;
       }
     }
-    if (whole < tail_begin) {
-      emit(s, whole, whole + num_k_blocks);
-      whole += num_k_blocks;
-      return true;
+    if (phase == 2) {
+      if (whole < tail_begin) {
+        emit(s, whole, whole + num_k_blocks);
+        whole += num_k_blocks;
+        return true;
+      }
+      phase = 3;
     }
-    return false;
+    if (next_tile >= dp_tiles) return false;
+    s.tile = next_tile;
+    s.sk_slot = 0;
+    s.kb_begin = 0;
+    s.kb_count = num_k_blocks;
+    s.contrib = 0;
+    s.n_contrib = 1;
+    next_tile += tile_step;
+    return true;
   }
 };
 
@@ -265,6 +297,35 @@ __device__ __forceinline__ void report_error(const GemmParams& p, volatile int* 
     p.status[3] = aux;
     __threadfence_system();
   }
+}
+
+// Stream-K fix-up of kN accumulator columns held by one thread (one row): replaces r[] by the
+// sum of all contributors' partials in contributor order, taking this contributor's own value
+// from r[] itself, so the result does not depend on which contributor arrived last.  `col_base`
+// points at this row's entry of the first of the kN columns in contributor 0's slot; consecutive
+// columns are `col_stride` floats apart and consecutive contributors `slot_stride`.
+template <int kN>
+__device__ __forceinline__ void sum_partials(uint32_t (&r)[kN], const float* col_base,
+                                             size_t col_stride, size_t slot_stride, int contrib,
+                                             int n_contrib) {
+  float sum[kN];
+#pragma unroll 1
+  for (int q = 0; q < n_contrib; ++q) {
+    float t[kN];
+    if (q == contrib) {
+#pragma unroll
+      for (int j = 0; j < kN; ++j) t[j] = __uint_as_float(r[j]);
+    } else {
+      // kN independent loads in flight per thread (one 128-byte line per warp each).
+      const float* src = col_base + static_cast<size_t>(q) * slot_stride;
+#pragma unroll
+      for (int j = 0; j < kN; ++j) t[j] = __ldcg(src + static_cast<size_t>(j) * col_stride);
+    }
+#pragma unroll
+    for (int j = 0; j < kN; ++j) sum[j] = (q == 0) ? t[j] : sum[j] + t[j];
+  }
+#pragma unroll
+  for (int j = 0; j < kN; ++j) r[j] = __float_as_uint(sum[j]);
 }
 
 template <class Cfg>
@@ -513,20 +574,20 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
       // ---- stream-K: publish this segment's partial; the last arriver finishes the rows ----
       bool finish = true;
       const float* tile_partials = nullptr;
-      if constexpr (Cfg::kEpiMode == kEpiDirect) {
+      {
         if (seg.n_contrib > 1) {
           // Slot layout [contributor][column][row] so that a warp's 32 rows of one column are
           // one 128-byte line.  Counters are per (tile, CTA of the pair, lane quadrant): the
           // four epilogue warps never have to synchronise with each other.
-          tile_partials = p.partials + static_cast<size_t>(seg.tile) * p.max_contrib *
+          tile_partials = p.partials + static_cast<size_t>(seg.sk_slot) * p.max_contrib *
                                            (static_cast<size_t>(BLOCK_N) * Cfg::TILE_M);
           float* mine = const_cast<float*>(tile_partials) +
                         static_cast<size_t>(seg.contrib) * BLOCK_N * Cfg::TILE_M +
                         cta_rank * Cfg::BLOCK_M + row_in_cta;
-          const long long slot_end = (static_cast<long long>(seg.tile) * p.max_contrib +
+          const long long slot_end = (static_cast<long long>(seg.sk_slot) * p.max_contrib +
                                       seg.contrib + 1) * (static_cast<long long>(BLOCK_N) * Cfg::TILE_M);
           const long long counter_idx =
-              (static_cast<long long>(seg.tile) * kCtaGroup + cta_rank) * 4 + quad;
+              (static_cast<long long>(seg.sk_slot) * kCtaGroup + cta_rank) * 4 + quad;
           const bool in_bounds = seg.contrib >= 0 && seg.contrib < p.max_contrib &&
                                  seg.n_contrib <= p.max_contrib && slot_end <= p.partials_elems &&
                                  counter_idx < p.counters_len;
@@ -575,6 +636,14 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
           tmem_ld_32x32b_x32(taddr + c, r0);
           tmem_ld_32x32b_x32(taddr + c + 32, r1);
           tmem_ld_wait();
+          if (tile_partials != nullptr) {
+            const float* base = tile_partials + static_cast<size_t>(c) * Cfg::TILE_M +
+                                cta_rank * Cfg::BLOCK_M + row_in_cta;
+            const size_t slot = static_cast<size_t>(BLOCK_N) * Cfg::TILE_M;
+            sum_partials<32>(r0, base, Cfg::TILE_M, slot, seg.contrib, seg.n_contrib);
+            sum_partials<32>(r1, base + 32 * Cfg::TILE_M, Cfg::TILE_M, slot, seg.contrib,
+                             seg.n_contrib);
+          }
           const uint32_t row_addr = buf + lane * 128u;
           const uint32_t sw = lane & 7u;
 #pragma unroll
@@ -623,28 +692,10 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
           tmem_ld_32x32b_x16(taddr + c, r);
           tmem_ld_wait();
           if (tile_partials != nullptr) {
-            // Sum the contributors in index order (own value from tensor memory) so the result
-            // does not depend on which contributor arrived last.
-            const float* col_base = tile_partials + static_cast<size_t>(c) * Cfg::TILE_M +
-                                    cta_rank * Cfg::BLOCK_M + row_in_cta;
-            float sum[16];
-#pragma unroll 1
-            for (int q = 0; q < seg.n_contrib; ++q) {
-              float t[16];
-              if (q == seg.contrib) {
-#pragma unroll
-                for (int j = 0; j < 16; ++j) t[j] = __uint_as_float(r[j]);
-              } else {
-                // 16 independent loads in flight per thread (one 128-byte line per warp each).
-                const float* src = col_base + static_cast<size_t>(q) * BLOCK_N * Cfg::TILE_M;
-#pragma unroll
-                for (int j = 0; j < 16; ++j) t[j] = __ldcg(src + static_cast<size_t>(j) * Cfg::TILE_M);
-              }
-#pragma unroll
-              for (int j = 0; j < 16; ++j) sum[j] = (q == 0) ? t[j] : sum[j] + t[j];
-            }
-#pragma unroll
-            for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(sum[j]);
+            sum_partials<16>(r, tile_partials + static_cast<size_t>(c) * Cfg::TILE_M +
+                                    cta_rank * Cfg::BLOCK_M + row_in_cta,
+                             Cfg::TILE_M, static_cast<size_t>(BLOCK_N) * Cfg::TILE_M, seg.contrib,
+                             seg.n_contrib);
           }
           const int col = col0 + c;
           if (transposed) {

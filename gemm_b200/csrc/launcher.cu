@@ -225,6 +225,8 @@ struct Plan {
   bool swap = false;        // X = the operand that indexes output COLUMNS of the stored matrix
   int cta_group = 1, block_n = 256, epi = kEpiTmaStore;
   bool stream_k = false;
+  int sk_first_tile = 0;    // tiles below are handed out round-robin, tiles from here on are cut
+  int sk_splits = 0;        // > 0: uniform k-chunks per cut tile (large kernels)
   int group_m = 8;
   int num_ctas = 0;
   int Md = 0, Nd = 0;
@@ -243,10 +245,20 @@ int round_block_n(int64_t n) {
   return 256;
 }
 
+// Into how many equal k-chunks the tiles of a last wave of `rest` tiles (of `workers`) are cut so
+// that every worker takes at most one chunk; 0 = leave the wave whole (it is more than half full,
+// or K is too short: a chunk must keep at least 8 k-blocks).
+int hybrid_splits(int rest, int workers, int num_k_blocks) {
+  if (rest <= 0) return 0;
+  int splits = workers / rest;            // k-chunks per tile so that every worker gets <= 1
+  splits = std::min(splits, num_k_blocks / 8);
+  return splits >= 2 ? std::min(splits, 8) : 0;
+}
+
 // pm x pn is the matrix as stored (row-major, pitch ldc): [M,N] for row-major C, [N,M] for the
 // reference's column-major C.
 int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int sm_count,
-              const Override& ov, Plan* plan) {
+              const Override& ov, Plan* plan, bool allow_hybrid = true) {
   Plan p;
   const bool tma_store_ok = (ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
 
@@ -286,8 +298,14 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
       const int64_t workers = std::max(1, sm_count / c.cta_group);
       const int64_t tm = 128 * c.cta_group;
       const int64_t tiles = ((md + tm - 1) / tm) * ((nd + c.block_n - 1) / c.block_n);
-      const int64_t waves = (tiles + workers - 1) / workers;
-      const double cost = static_cast<double>(waves) * 128.0 * c.block_n / c.speed;
+      const int rest = static_cast<int>(tiles % workers);
+      double waves = static_cast<double>(tiles / workers);
+      if (rest > 0) {
+        const int cut = allow_hybrid && ov.stream_k != 0
+            ? hybrid_splits(rest, static_cast<int>(workers), static_cast<int>((K + 63) / 64)) : 0;
+        waves += cut > 0 ? 1.0 / cut + 0.05 : 1.0;
+      }
+      const double cost = waves * 128.0 * c.block_n / c.speed;
       if (best == 0.0 || cost < best) {
         best = cost;
         best_group = c.cta_group;
@@ -316,31 +334,50 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
   p.group_m = std::max(1, std::min(p.group_m, p.num_m_tiles));
 
   const int workers_max = std::max(1, sm_count / cta_group);
-  // Stream-K: only for the direct-store (skinny) kernels, when whole tiles cannot fill or
-  // balance the machine and there is enough K to cut.
-  bool stream_k = (epi == kEpiDirect) && (block_n <= 128) && (p.num_k_blocks >= 8) &&
-                  (p.num_tiles % workers_max != 0) && (p.num_tiles < 8 * workers_max);
-  if (ov.stream_k >= 0) stream_k = (ov.stream_k != 0) && (epi == kEpiDirect);
-  p.stream_k = stream_k;
-
   int workers = workers_max;
   if (ov.max_ctas > 0) workers = std::max(1, std::min(workers, ov.max_ctas / cta_group));
+
+  // Schedule.
+  //  * Direct-store (skinny) kernels: stream-K over ALL tiles when whole tiles cannot fill or
+  //    balance the machine and there is enough K to cut.
+  //  * TMA-store kernels: whole waves of tiles go round-robin; a last, partly filled wave is cut
+  //    stream-K style among all workers when that shortens the launch (wave quantisation:
+  //    4096^3 is 3.46 waves of pair tiles).
+  bool stream_k = false;
+  int sk_first = 0, sk_splits = 0;
+  if (epi == kEpiDirect) {
+    stream_k = (block_n <= 128) && (p.num_k_blocks >= 8) && (p.num_tiles % workers_max != 0) &&
+               (p.num_tiles < 8 * workers_max);
+    if (ov.stream_k >= 0) stream_k = (ov.stream_k != 0);
+  } else {
+    const int rest = p.num_tiles % workers;
+    sk_splits = allow_hybrid && ov.stream_k != 0 ? hybrid_splits(rest, workers, p.num_k_blocks) : 0;
+    stream_k = sk_splits > 0;
+    sk_first = p.num_tiles - rest;
+  }
+  const int sk_tiles = stream_k ? p.num_tiles - sk_first : 0;
   if (stream_k &&
-      static_cast<size_t>(p.num_tiles) * cta_group * 4 * sizeof(int) > kCounterRegionBytes) {
+      static_cast<size_t>(sk_tiles) * cta_group * 4 * sizeof(int) > kCounterRegionBytes) {
     if (ov.stream_k > 0) return NEOGEMM_ERR_UNSUPPORTED;
     stream_k = false;
-    p.stream_k = false;
   }
+  p.stream_k = stream_k;
+  p.sk_first_tile = stream_k ? sk_first : 0;
+  p.sk_splits = stream_k ? sk_splits : 0;
   if (stream_k) {
-    const int64_t units = static_cast<int64_t>(p.num_tiles) * p.num_k_blocks;
-    workers = static_cast<int>(std::min<int64_t>(workers, units));
-    const int64_t per = units / workers;  // >= 1
-    p.max_contrib = static_cast<int>((p.num_k_blocks + per - 1) / per) + 1;
+    const int64_t units = static_cast<int64_t>(sk_tiles) * p.num_k_blocks;
+    if (sk_splits > 0) {
+      p.max_contrib = sk_splits;
+    } else {
+      workers = static_cast<int>(std::min<int64_t>(workers, units));
+      const int64_t per = std::max<int64_t>(1, units / workers);
+      p.max_contrib = static_cast<int>((p.num_k_blocks + per - 1) / per) + 1;
+    }
     // The arrival counters always occupy the same fixed region at the start of a workspace, so
     // that launches of different shapes sharing one workspace never see each other's partials
     // where they expect zeroed counters.
     p.counters_bytes = kCounterRegionBytes;
-    p.partials_bytes = static_cast<size_t>(p.num_tiles) * p.max_contrib * block_n * tile_m *
+    p.partials_bytes = static_cast<size_t>(sk_tiles) * p.max_contrib * block_n * tile_m *
                        sizeof(float);
   } else {
     workers = std::min(workers, p.num_tiles);
@@ -491,6 +528,8 @@ int gemm_device(const void* A, const void* B, void* C, int64_t M, int64_t N, int
   params.out_stride_r = plan.swap ? 1 : ldc;
   params.out_stride_c = plan.swap ? ldc : 1;
   params.stream_k = plan.stream_k ? 1 : 0;
+  params.sk_first_tile = plan.sk_first_tile;
+  params.sk_splits = plan.sk_splits;
   params.max_contrib = plan.max_contrib;
   params.status = st->status_dev;
   params.timers = nullptr;
@@ -714,7 +753,7 @@ int neogemm_debug_plan(int64_t M, int64_t N, int64_t K, int64_t ldc, int c_col_m
   const int fields[16] = {plan.cta_group, plan.block_n, plan.kernel->stages, plan.swap ? 1 : 0,
                           plan.stream_k ? 1 : 0, plan.num_ctas, plan.num_tiles, plan.group_m,
                           plan.epi, plan.Md, plan.Nd, plan.num_m_tiles, plan.num_n_tiles,
-                          plan.num_k_blocks, plan.max_contrib, 0};
+                          plan.num_k_blocks, plan.max_contrib, plan.sk_first_tile};
   for (int i = 0; i < 16; ++i) plan_out[i] = fields[i];
   GemmParams params;
   std::memset(&params, 0, sizeof(params));
@@ -724,6 +763,8 @@ int neogemm_debug_plan(int64_t M, int64_t N, int64_t K, int64_t ldc, int c_col_m
   params.num_k_blocks = plan.num_k_blocks;
   params.group_m = plan.group_m;
   params.stream_k = plan.stream_k ? 1 : 0;
+  params.sk_first_tile = plan.sk_first_tile;
+  params.sk_splits = plan.sk_splits;
   const int workers = plan.num_ctas / plan.cta_group;
   int count = 0;
   for (int w = 0; w < workers; ++w) {
@@ -742,5 +783,6 @@ int neogemm_debug_plan(int64_t M, int64_t N, int64_t K, int64_t ldc, int c_col_m
   }
   return count;
 }
+
 
 }  // extern "C"

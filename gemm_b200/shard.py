@@ -63,3 +63,53 @@ def sharded_matmul(A_block: torch.Tensor, B: Optional[torch.Tensor], N: int, K: 
     parts = [torch.empty_like(padded) for _ in range(world)]
     dist.all_gather(parts, padded, group=group)
     return torch.cat([p[:int(n)] for p, n in zip(parts, sizes)], dim=0), B_local
+
+
+def sharded_matmul_overlapped(A_block: torch.Tensor, B: Optional[torch.Tensor], N: int, K: int,
+                              chunks: int = 4, group=None, src: int = 0,
+                              matmul_out: Optional[Callable] = None):
+    """Same product with the broadcast of B hidden under compute: B travels in ``chunks`` row
+    blocks on a side stream, and the product for the columns of C that a block feeds is launched
+    as soon as that block has landed in local HBM.  The kernel still reads local memory only.
+
+    Returns (C_block, B_local).  ``matmul_out(A, B_rows, out)`` defaults to the CUDA operator
+    writing into a column slice of C (row pitch N); CPU tests inject a stand-in."""
+    import torch.distributed as dist
+    if matmul_out is None:
+        from .ops import matmul as _mm
+
+        def matmul_out(a, b, out):  # noqa: ANN001
+            _mm(a, b, out=out)
+    rank = dist.get_rank(group)
+    if rank == src:
+        if B is None or tuple(B.shape) != (N, K):
+            raise ValueError(f"rank {src} must supply B with shape [{N},{K}]")
+        B_local = B
+    else:
+        B_local = torch.empty((N, K), dtype=A_block.dtype, device=A_block.device)
+    C_block = torch.empty((A_block.shape[0], N), dtype=A_block.dtype, device=A_block.device)
+    # Column blocks on multiples of 256 (one tile) so that every launch sees whole tiles.
+    chunks = max(1, min(chunks, (N + 255) // 256))
+    per = ((N + chunks - 1) // chunks + 255) // 256 * 256
+    bounds = [(n0, min(n0 + per, N)) for n0 in range(0, N, per)]
+    on_gpu = A_block.is_cuda
+    if on_gpu:
+        compute = torch.cuda.current_stream(A_block.device)
+        side = torch.cuda.Stream(device=A_block.device)
+        side.wait_stream(compute)
+        events = []
+        with torch.cuda.stream(side):
+            for n0, n1 in bounds:
+                dist.broadcast(B_local[n0:n1], src=src, group=group)
+                ev = torch.cuda.Event()
+                ev.record(side)
+                events.append(ev)
+        for (n0, n1), ev in zip(bounds, events):
+            compute.wait_event(ev)
+            matmul_out(A_block, B_local[n0:n1], C_block[:, n0:n1])
+        B_local.record_stream(side)
+    else:
+        for n0, n1 in bounds:
+            dist.broadcast(B_local[n0:n1], src=src, group=group)
+            matmul_out(A_block, B_local[n0:n1], C_block[:, n0:n1])
+    return C_block, B_local

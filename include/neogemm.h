@@ -98,7 +98,8 @@ const char* neogemm_status_str(int status);
 
 /* Kernel configuration chosen by the most recent neogemm_bf16_nt() on this thread:
  * out[0] = CTAs per tile (1 or 2), out[1] = tile columns (UMMA N), out[2] = ring stages,
- * out[3] = 1 if operands were swapped (B rows on the 128-lane axis), out[4] = 1 if stream-K,
+ * out[3] = 1 if operands were swapped (B rows on the 128-lane axis), out[4] = 1 if stream-K
+ * (all tiles for skinny shapes, the last partly filled wave for large ones),
  * out[5] = CTAs launched, out[6] = tiles, out[7] = raster group height. */
 int neogemm_last_config(int out[8]);
 
@@ -135,7 +136,7 @@ int neogemm_set_phase_timers(void* device_buffer, size_t bytes);
  * and walks the kernel's own work iterator on the host.
  *   plan_out[16]: CTAs per tile, tile columns, stages, swap, stream-K, CTAs, tiles, raster group,
  *                 epilogue (0 TMA store, 1 direct), Md, Nd, tile rows, tile columns, k-blocks,
- *                 partial slots per tile, 0.
+ *                 partial slots per tile, first tile of the stream-K region.
  *   segments: up to max_segments records of 8 ints {worker, tile, first k-block, k-blocks,
  *                 contributor index, contributors, tile row, tile column} (may be NULL).
  * Returns the number of segments, or minus a neogemm_status code.  No counterpart in the

@@ -41,3 +41,26 @@ def test_pair_kernel_is_deterministic():
         ops.set_override()
     torch.cuda.synchronize()
     assert ops.device_status()[0] == 0
+
+
+@pytest.mark.parametrize("cta_group,block_n", [(2, 256), (2, 128), (1, 256), (1, 128)])
+def test_cut_last_wave_on_every_tma_store_kernel(cta_group, block_n):
+    # Force the stream-K treatment of the last, partly filled wave (ragged shape, several waves).
+    ov = dict(cta_group=cta_group, block_n=block_n, swap=0, stream_k=1)
+    stats, cfg = run_case(3000, 5000, 1024, override=ov)
+    assert cfg["stream_k"] == 1 and cfg["cta_group"] == cta_group, cfg
+    run_case(1000, 520, 2048, override=ov, col_major=True)
+
+
+def test_cut_last_wave_is_chosen_for_4096_cube_and_is_deterministic():
+    from gemm_b200.inputs import make_problem
+    stats, cfg = run_case(4096, 4096, 4096)
+    assert (cfg["cta_group"], cfg["block_n"], cfg["stream_k"]) == (2, 256, 1), cfg
+    A, B = make_problem(4096, 4096, 2048, seed=6)
+    dA, dB = A.cuda(), B.cuda()
+    first = ops.matmul(dA, dB).clone()
+    assert ops.last_config()["stream_k"] == 1
+    for _ in range(10):
+        assert torch.equal(first.view(torch.int16), ops.matmul(dA, dB).view(torch.int16))
+    torch.cuda.synchronize()
+    assert ops.device_status()[0] == 0

@@ -12,7 +12,7 @@ from gemm_b200.inputs import make_problem, make_row_block, make_tall_operand
 
 lib.neogemm_debug_plan.restype = ctypes.c_int
 PLAN_KEYS = ("cta_group", "block_n", "stages", "swap", "stream_k", "ctas", "tiles", "group_m",
-             "epi", "Md", "Nd", "m_tiles", "n_tiles", "k_blocks", "max_contrib")
+             "epi", "Md", "Nd", "m_tiles", "n_tiles", "k_blocks", "max_contrib", "sk_first")
 
 
 def plan(M, N, K, ldc=None, col_major=False, sm=148, override=None, max_seg=400000):
@@ -144,3 +144,41 @@ def test_inputs_are_deterministic_and_scaled():
     assert torch.equal(blk.view(torch.int16), tall.view(torch.int16))
     with pytest.raises(ValueError):
         make_tall_operand(10, 64, first_row=5)
+
+
+def test_last_partial_wave_of_large_shapes_is_cut():
+    # 4096^3: 256 pair tiles on 74 pairs = 3 whole waves (222 tiles) + 34 tiles, each cut into
+    # two k-halves so that 68 of the 74 workers take one half: 3.5 waves instead of 4.
+    p, segs = plan(4096, 4096, 4096)
+    assert (p["cta_group"], p["block_n"], p["stream_k"], p["sk_first"]) == (2, 256, 1, 222)
+    assert p["max_contrib"] == 2
+    check_cover(p, segs)
+    per_worker = defaultdict(int)
+    for s in segs:
+        per_worker[s[0]] += s[3]
+    assert sorted(set(per_worker.values())) == [192, 224] and len(per_worker) == 74
+    assert sum(1 for v in per_worker.values() if v == 224) == 68
+    # the cut segment comes first in a worker's sequence, and chunk i of every tile covers the
+    # same k range (that is what keeps panel sharing in L2)
+    first_seen = {}
+    for s in segs:
+        first_seen.setdefault(s[0], s)
+    cut = [s for s in first_seen.values() if s[1] >= 222]
+    assert len(cut) == 68
+    assert {(s[4], s[2], s[3]) for s in cut} == {(0, 0, 32), (1, 32, 32)}
+    # 8192^3 (13.84 waves) keeps whole tiles: its last wave is more than half full
+    p, segs = plan(8192, 8192, 8192)
+    assert p["stream_k"] == 0
+    check_cover(p, segs)
+    p, segs = plan(4096, 4096, 4096, override=(-1, -1, -1, 0, -1, -1))
+    assert p["stream_k"] == 0
+    check_cover(p, segs)
+
+
+@pytest.mark.parametrize("shape", [(2048, 2048, 2048), (3000, 5000, 1024), (4096, 4096, 512),
+                                   (1280, 1280, 8192), (131072, 8192, 8192)])
+@pytest.mark.parametrize("override", [None, (1, 256, 0, 1, -1, -1), (2, 128, 0, 1, -1, -1),
+                                      (1, 128, 0, 1, -1, 40)])
+def test_hybrid_schedules_cover_the_problem(shape, override):
+    p, segs = plan(*shape, override=override)
+    check_cover(p, segs)

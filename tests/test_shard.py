@@ -87,3 +87,35 @@ def test_rank_zero_must_supply_b(tmp_path):
                            matmul=lambda a, b: a.float() @ b.float().t())
     finally:
         dist.destroy_process_group()
+
+
+def _worker_overlap(rank, world, port, M, N, K, out_dir):
+    import torch.distributed as dist
+    from gemm_b200.inputs import make_problem
+    from gemm_b200.shard import row_partition, sharded_matmul_overlapped
+    from oracle import oracle
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        A, B = make_problem(M, N, K, seed=5)
+        r0, r1 = row_partition(M, world, rank)
+
+        def stand_in(a, b, out):
+            out.copy_(oracle.gemm_bf16(a, b.contiguous()))
+        C_block, B_local = sharded_matmul_overlapped(A[r0:r1].contiguous(), B if rank == 0 else None,
+                                                     N, K, chunks=3, matmul_out=stand_in)
+        assert torch.equal(B_local.view(torch.int16), B.view(torch.int16))
+        want = oracle.gemm_bf16(A, B)[r0:r1]
+        assert torch.equal(C_block.view(torch.int16), want.contiguous().view(torch.int16))
+        open(os.path.join(out_dir, f"ok{rank}"), "w").close()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(180)
+def test_overlapped_broadcast_on_two_gloo_ranks(tmp_path):
+    world = 2
+    mp.spawn(_worker_overlap, args=(world, _free_port(), 200, 700, 64, str(tmp_path)),
+             nprocs=world, join=True)
+    assert all((tmp_path / f"ok{r}").exists() for r in range(world))
