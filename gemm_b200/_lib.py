@@ -36,6 +36,9 @@ def _load() -> ctypes.CDLL:
     lib.neogemm_bf16_nt.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                     c_int64, c_int64, c_int64, c_int, c_void_p, c_size_t,
                                     c_void_p]
+    lib.neogemm_bf16_nt_noalloc.restype = c_int
+    lib.neogemm_bf16_nt_noalloc.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                                            c_int64, c_int64, c_int64, c_int64, c_int, c_void_p]
     lib.neogemm_workspace_bytes.restype = c_size_t
     lib.neogemm_workspace_bytes.argtypes = [c_int64, c_int64, c_int64, c_int]
     lib.neogemm_bf16_nt_host.restype = c_int

@@ -785,4 +785,198 @@ int neogemm_debug_plan(int64_t M, int64_t N, int64_t K, int64_t ldc, int c_col_m
 }
 
 
+// ------------------------------------------------------------------------------------------
+// Entry point that allocates nothing.
+//
+// Who needs it: code that must not (or cannot) ask the CUDA allocator for memory at the moment
+// it multiplies - a serving loop whose memory pool already owns the whole device, a real-time
+// path where an allocation's latency or failure is unacceptable, a plugin that is forbidden to
+// touch the process's allocator.  neogemm_bf16_nt() may allocate on its first call per device
+// (a pinned status word) and whenever a skinny shape needs a larger library-owned stream-K
+// workspace; this variant never does.  Its stream-K scratch is the fixed array below, which
+// every GPU that loads the library carries until the process exits.
+// ------------------------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kStaticScratchBytes = 32u << 20;   // 32 MiB: counters (256 KiB) + partials
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+static __device__ __align__(16) int g_static_status[4];
+
+struct StaticState {
+  bool ready = false;
+  int init_error = NEOGEMM_OK;
+  unsigned char* scratch = nullptr;   // DEVICE address of g_static_scratch on this device
+  int* status = nullptr;              // DEVICE address of g_static_status on this device
+  DeviceState launch_state;           // only sm_count and the per-kernel attribute flags are used
+};
+StaticState g_static[kMaxDevices];
+PFN_cuTensorMapEncodeTiled_v12000 g_static_encode = nullptr;
+
+// In host code the names g_static_scratch / g_static_status are host-side stand-ins, not device
+// addresses; the addresses a kernel may use come from cudaGetSymbolAddress, once per device,
+// with that device current.  Called with g_mu held.
+StaticState* static_state(int* code) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    cudaGetLastError();
+    *code = NEOGEMM_ERR_UNSUPPORTED;
+    return nullptr;
+  }
+  StaticState& st = g_static[dev];
+  if (st.ready) {
+    *code = st.init_error;
+    return st.init_error == NEOGEMM_OK ? &st : nullptr;
+  }
+  st.ready = true;
+  int major = 0;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess ||
+      major != 10 ||
+      cudaDeviceGetAttribute(&st.launch_state.sm_count, cudaDevAttrMultiProcessorCount, dev) !=
+          cudaSuccess) {
+    cudaGetLastError();
+    st.init_error = NEOGEMM_ERR_UNSUPPORTED;
+  } else if (g_static_encode == nullptr) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) ==
+            cudaSuccess && q == cudaDriverEntryPointSuccess) {
+      g_static_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+    } else {
+      cudaGetLastError();
+      st.init_error = NEOGEMM_ERR_DESCRIPTOR;
+    }
+  }
+  if (st.init_error == NEOGEMM_OK) {
+    void* scratch = nullptr;
+    void* status = nullptr;
+    if (cudaGetSymbolAddress(&scratch, g_static_scratch) != cudaSuccess ||
+        cudaGetSymbolAddress(&status, g_static_status) != cudaSuccess || scratch == nullptr ||
+        status == nullptr) {
+      cudaGetLastError();
+      st.init_error = NEOGEMM_ERR_CUDA;
+    } else {
+      st.scratch = static_cast<unsigned char*>(scratch);
+      st.status = static_cast<int*>(status);
+    }
+  }
+  *code = st.init_error;
+  return st.init_error == NEOGEMM_OK ? &st : nullptr;
+}
+
+// Same geometry as get_tensor_map(), encoded straight into the caller's variable: no cache, so no
+// host heap growth either.
+int encode_map_uncached(const void* base, uint64_t inner, uint64_t rows, uint64_t pitch_bytes,
+                        uint32_t box_rows, int for_store, CUtensorMap* out) {
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (pitch_bytes & 15) != 0 ||
+      pitch_bytes >= (1ull << 40) || inner == 0 || rows == 0 || inner > 0xffffffffull ||
+      rows > 0xffffffffull || box_rows == 0 || box_rows > 256) {
+    return NEOGEMM_ERR_UNSUPPORTED;
+  }
+  cuuint64_t dims[2] = {inner, rows};
+  cuuint64_t strides[1] = {pitch_bytes};
+  cuuint32_t box[2] = {64, box_rows};
+  cuuint32_t elem_strides[2] = {1, 1};
+  const CUresult r = g_static_encode(
+      out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+      elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+      for_store ? CU_TENSOR_MAP_L2_PROMOTION_NONE : CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? NEOGEMM_OK : NEOGEMM_ERR_DESCRIPTOR;
+}
+
+}  // namespace
+
+int neogemm_bf16_nt_noalloc(const void* A, const void* B, void* C, int64_t M, int64_t N,
+                            int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int c_col_major,
+                            void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  int rc = validate(A, B, C, M, N, K, lda, ldb, ldc, c_col_major);
+  if (rc != NEOGEMM_OK) return rc;
+  if (M == 0 || N == 0) return NEOGEMM_OK;
+
+  std::lock_guard<std::mutex> lock(g_mu);
+  StaticState* st = static_state(&rc);
+  if (st == nullptr) return rc;
+
+  const int64_t pm = c_col_major ? N : M;
+  const int64_t pn = c_col_major ? M : N;
+  if (K == 0) {
+    if (cudaMemset2DAsync(C, static_cast<size_t>(ldc) * 2, 0, static_cast<size_t>(pn) * 2,
+                          static_cast<size_t>(pm), stream) != cudaSuccess) {
+      cudaGetLastError();
+      return NEOGEMM_ERR_CUDA;
+    }
+    return NEOGEMM_OK;
+  }
+  const void* U = c_col_major ? B : A;
+  const void* V = c_col_major ? A : B;
+  const int64_t ldu = c_col_major ? ldb : lda;
+  const int64_t ldv = c_col_major ? lda : ldb;
+
+  Plan plan;
+  const Override no_override;
+  // Only the skinny (direct-store) kernels take scratch here: the cut last wave of the large
+  // kernels is left off, so that large shapes never depend on the fixed array's size.
+  rc = make_plan(pm, pn, K, ldc, C, st->launch_state.sm_count, no_override, &plan, false);
+  if (rc != NEOGEMM_OK) return rc;
+  if (plan.stream_k && plan.counters_bytes + plan.partials_bytes > kStaticScratchBytes)
+    return NEOGEMM_ERR_WORKSPACE;   // beyond the fixed scratch: use neogemm_bf16_nt()
+
+  const void* X = plan.swap ? V : U;
+  const void* Y = plan.swap ? U : V;
+  const int64_t ldx = plan.swap ? ldv : ldu;
+  const int64_t ldy = plan.swap ? ldu : ldv;
+  CUtensorMap mx, my, md;
+  std::memset(&md, 0, sizeof(md));
+  rc = encode_map_uncached(X, static_cast<uint64_t>(K), static_cast<uint64_t>(plan.Md),
+                           static_cast<uint64_t>(ldx) * 2, 128, 0, &mx);
+  if (rc != NEOGEMM_OK) return rc;
+  rc = encode_map_uncached(Y, static_cast<uint64_t>(K), static_cast<uint64_t>(plan.Nd),
+                           static_cast<uint64_t>(ldy) * 2,
+                           static_cast<uint32_t>(plan.block_n / plan.cta_group), 0, &my);
+  if (rc != NEOGEMM_OK) return rc;
+  if (plan.epi == kEpiTmaStore) {
+    rc = encode_map_uncached(C, static_cast<uint64_t>(plan.Nd), static_cast<uint64_t>(plan.Md),
+                             static_cast<uint64_t>(ldc) * 2, 32, 1, &md);
+    if (rc != NEOGEMM_OK) return rc;
+  }
+
+  GemmParams params;
+  std::memset(&params, 0, sizeof(params));
+  params.Md = plan.Md;
+  params.Nd = plan.Nd;
+  params.K = static_cast<int>(K);
+  params.num_m_tiles = plan.num_m_tiles;
+  params.num_n_tiles = plan.num_n_tiles;
+  params.num_tiles = plan.num_tiles;
+  params.num_k_blocks = plan.num_k_blocks;
+  params.group_m = plan.group_m;
+  params.l2_hints = kDefaultTuning[0];
+  params.epi_wait_hint_ns = kDefaultTuning[1];
+  params.main_wait_hint_ns = kDefaultTuning[2];
+  params.out = static_cast<__nv_bfloat16*>(C);
+  params.out_stride_r = plan.swap ? 1 : ldc;
+  params.out_stride_c = plan.swap ? ldc : 1;
+  params.out_span = (pm - 1) * ldc + pn;
+  params.stream_k = plan.stream_k ? 1 : 0;
+  params.sk_first_tile = plan.sk_first_tile;
+  params.sk_splits = plan.sk_splits;
+  params.max_contrib = plan.max_contrib;
+  params.status = st->status;
+  params.timers = nullptr;
+  if (plan.stream_k) {
+    // Every call shares the array and it keeps the previous call's contents: the arrival
+    // counters must start at zero, so clear their region in stream order before the launch.
+    if (cudaMemsetAsync(st->scratch, 0, plan.counters_bytes, stream) != cudaSuccess) {
+      cudaGetLastError();
+      return NEOGEMM_ERR_CUDA;
+    }
+    params.tile_counters = reinterpret_cast<int*>(st->scratch);
+    params.partials = reinterpret_cast<float*>(st->scratch + plan.counters_bytes);
+    params.counters_len = static_cast<long long>(plan.counters_bytes / sizeof(int));
+    params.partials_elems = static_cast<long long>(plan.partials_bytes / sizeof(float));
+  }
+  return launch(&st->launch_state, plan, mx, my, md, params, stream);
+}
+
 }  // extern "C"

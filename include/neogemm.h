@@ -67,6 +67,34 @@ int neogemm_bf16_nt(const void* A, const void* B, void* C,
                     void* workspace, size_t workspace_bytes,
                     void* stream);
 
+/* The same product for callers that must not allocate: it calls no cudaMalloc, cudaFree,
+ * cudaHostAlloc or any other allocating routine, on any call.  (No counterpart in the reference.)
+ *
+ * Meant for code that cannot ask the CUDA allocator for memory when it multiplies: a serving
+ * loop whose own pool already holds the whole device, a latency-critical path that cannot afford
+ * an allocation or its failure, a plugin that may not touch the host process's allocator.
+ * neogemm_bf16_nt() can allocate (a pinned status word on its first call per device, and a
+ * library-owned workspace when a skinny shape takes the stream-K schedule); this one uses a fixed
+ * 32 MiB array compiled into the library as its stream-K scratch, which every GPU that loads
+ * libneogemm.so holds until the process exits.
+ *
+ * Arguments as for neogemm_bf16_nt(), without the workspace pair.  Differences:
+ *   - a shape whose stream-K scratch would exceed the 32 MiB returns NEOGEMM_ERR_WORKSPACE
+ *     (the benchmark's largest skinny shape, M=128 N=28672 K=8192, needs 29.6 MiB and fits);
+ *   - the first call on each device looks up the device address of the array
+ *     (cudaGetSymbolAddress) and the driver's tensor-map encoder; make that first call before
+ *     starting any stream capture;
+ *   - all calls on a device share the one array: calls whose kernels may overlap on the GPU
+ *     (different streams) race on it - serialise them, or use neogemm_bf16_nt() with separate
+ *     workspaces.  The part that must start at zero is cleared in stream order by every call;
+ *   - device-side bounded-wait failures are recorded in a word inside the library that
+ *     neogemm_device_status() does not show; thread-local overrides and tuning knobs are ignored.
+ */
+int neogemm_bf16_nt_noalloc(const void* A, const void* B, void* C,
+                            int64_t M, int64_t N, int64_t K,
+                            int64_t lda, int64_t ldb, int64_t ldc,
+                            int c_col_major, void* stream);
+
 /* Upper bound on the workspace neogemm_bf16_nt() may need for this shape on the current device
  * (0 when the data-parallel schedule would be chosen).  No counterpart in the reference, which
  * has no split-K. */
