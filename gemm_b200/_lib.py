@@ -36,6 +36,11 @@ def _load() -> ctypes.CDLL:
     lib.neogemm_bf16_nt.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                     c_int64, c_int64, c_int64, c_int, c_void_p, c_size_t,
                                     c_void_p]
+    lib.neogemm_bf16_nt_fused.restype = c_int
+    lib.neogemm_bf16_nt_fused.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
+                                          c_int64, c_int64, c_int64, c_int, ctypes.c_float,
+                                          ctypes.c_float, c_void_p, c_int, c_void_p, c_size_t,
+                                          c_void_p]
     lib.neogemm_bf16_nt_noalloc.restype = c_int
     lib.neogemm_bf16_nt_noalloc.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                             c_int64, c_int64, c_int64, c_int64, c_int, c_void_p]

@@ -69,6 +69,14 @@ struct GemmParams {
   float* partials;           // [stream-K tiles][max_contrib][BLOCK_N][TILE_M] fp32
   int* tile_counters;        // [stream-K tiles][kCtaGroup][4], zero before launch; the last arriver
                              // of each entry re-zeroes it
+  // Fused epilogue  D = act(alpha * (X Y^T) + beta * C_in + bias)  (all off: fuse == 0).
+  // The reference declares alpha/beta kernel parameters but never uses them (neogemmv4.cu:166).
+  int fuse;                  // 0: plain store; 1: apply the fields below
+  float alpha, beta;
+  const __nv_bfloat16* c_in; // read with the strides of `out` when beta != 0 (may alias `out`)
+  const __nv_bfloat16* bias; // null, or one bf16 per output column of C = A B^T (length N)
+  int bias_on_rows;          // 1: the bias index runs along the rows of D, 0: along its columns
+  int activation;            // 0 none, 1 ReLU, 2 GELU (tanh form)
   // Extents for the self-checks of every global access the kernel computes itself.
   long long partials_elems, counters_len, out_span;
   // Optional phase timers (null in production): 16 int64 per CTA, see PhaseTimer below.
@@ -296,6 +304,35 @@ __device__ __forceinline__ void report_error(const GemmParams& p, volatile int* 
     p.status[2] = seg;
     p.status[3] = aux;
     __threadfence_system();
+  }
+}
+
+// Fused epilogue on kN consecutive columns [col, col + kN) of one row of D held in r[] (fp32
+// bit patterns), in place.  Reads of C_in and bias are bounds-checked against Md / Nd.
+template <int kN>
+__device__ __forceinline__ void fused_epilogue(uint32_t (&r)[kN], const GemmParams& p, int row,
+                                               int col) {
+  const bool row_ok = row < p.Md;
+  float row_bias = 0.f;
+  if (p.bias != nullptr && p.bias_on_rows && row_ok) row_bias = __bfloat162float(p.bias[row]);
+  const __nv_bfloat16* cin = nullptr;
+  if (p.beta != 0.f && row_ok)
+    cin = p.c_in + static_cast<long long>(row) * p.out_stride_r;
+#pragma unroll
+  for (int j = 0; j < kN; ++j) {
+    float v = p.alpha * __uint_as_float(r[j]);
+    const bool ok = row_ok && (col + j) < p.Nd;
+    if (cin != nullptr && ok)
+      v += p.beta * __bfloat162float(cin[static_cast<long long>(col + j) * p.out_stride_c]);
+    if (p.bias != nullptr && ok)
+      v += p.bias_on_rows ? row_bias : __bfloat162float(p.bias[col + j]);
+    if (p.activation == 1) {
+      v = fmaxf(v, 0.f);
+    } else if (p.activation == 2) {
+      const float u = 0.7978845608028654f * (v + 0.044715f * v * v * v);
+      v = 0.5f * v * (1.f + tanhf(u));
+    }
+    r[j] = __float_as_uint(v);
   }
 }
 
@@ -644,6 +681,10 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
             sum_partials<32>(r1, base + 32 * Cfg::TILE_M, Cfg::TILE_M, slot, seg.contrib,
                              seg.n_contrib);
           }
+          if (p.fuse) {
+            fused_epilogue<32>(r0, p, row0 + row_in_cta, col0 + c);
+            fused_epilogue<32>(r1, p, row0 + row_in_cta, col0 + c + 32);
+          }
           const uint32_t row_addr = buf + lane * 128u;
           const uint32_t sw = lane & 7u;
 #pragma unroll
@@ -698,6 +739,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
                              seg.n_contrib);
           }
           const int col = col0 + c;
+          if (p.fuse) fused_epilogue<16>(r, p, row, col);
           if (transposed) {
 #pragma unroll
             for (int j = 0; j < 16; ++j)

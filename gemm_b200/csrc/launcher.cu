@@ -457,12 +457,21 @@ int launch(DeviceState* st, const Plan& plan, const CUtensorMap& mx, const CUten
   return NEOGEMM_OK;
 }
 
+// Optional fused epilogue: C = act(alpha * A B^T + beta * C + bias).
+struct Fusion {
+  bool on = false;
+  float alpha = 1.f, beta = 0.f;
+  const void* bias = nullptr;   // bf16[N] or null
+  int activation = 0;           // 0 none, 1 ReLU, 2 GELU (tanh form)
+};
+
 int gemm_device(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
                 int64_t lda, int64_t ldb, int64_t ldc, int c_col_major, void* workspace,
-                size_t workspace_bytes, cudaStream_t stream) {
+                size_t workspace_bytes, cudaStream_t stream, const Fusion& fusion = Fusion()) {
   int rc = validate(A, B, C, M, N, K, lda, ldb, ldc, c_col_major);
   if (rc != NEOGEMM_OK) return rc;
   if (M == 0 || N == 0) return NEOGEMM_OK;
+  if (fusion.on && K == 0) return NEOGEMM_ERR_UNSUPPORTED;
 
   DeviceState* st;
   {
@@ -532,6 +541,17 @@ int gemm_device(const void* A, const void* B, void* C, int64_t M, int64_t N, int
   params.sk_splits = plan.sk_splits;
   params.max_contrib = plan.max_contrib;
   params.status = st->status_dev;
+  if (fusion.on) {
+    params.fuse = 1;
+    params.alpha = fusion.alpha;
+    params.beta = fusion.beta;
+    params.c_in = static_cast<const __nv_bfloat16*>(C);
+    params.bias = static_cast<const __nv_bfloat16*>(fusion.bias);
+    // The bias runs along N.  N is the row axis of D when exactly one of "column-major C" and
+    // "operands swapped" holds.
+    params.bias_on_rows = ((c_col_major != 0) != plan.swap) ? 1 : 0;
+    params.activation = fusion.activation;
+  }
   params.timers = nullptr;
   if (t_timers != nullptr &&
       t_timers_bytes >= static_cast<size_t>(plan.num_ctas) * 16 * sizeof(long long))
@@ -595,6 +615,22 @@ int neogemm_bf16_nt(const void* A, const void* B, void* C, int64_t M, int64_t N,
                     size_t workspace_bytes, void* stream) {
   return gemm_device(A, B, C, M, N, K, lda, ldb, ldc, c_col_major, workspace, workspace_bytes,
                      static_cast<cudaStream_t>(stream));
+}
+
+int neogemm_bf16_nt_fused(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                          int64_t lda, int64_t ldb, int64_t ldc, int c_col_major, float alpha,
+                          float beta, const void* bias, int activation, void* workspace,
+                          size_t workspace_bytes, void* stream) {
+  if (activation < 0 || activation > 2) return NEOGEMM_ERR_BAD_ARG;
+  if (bias != nullptr && (reinterpret_cast<uintptr_t>(bias) & 1) != 0) return NEOGEMM_ERR_BAD_ARG;
+  Fusion f;
+  f.on = true;
+  f.alpha = alpha;
+  f.beta = beta;
+  f.bias = bias;
+  f.activation = activation;
+  return gemm_device(A, B, C, M, N, K, lda, ldb, ldc, c_col_major, workspace, workspace_bytes,
+                     static_cast<cudaStream_t>(stream), f);
 }
 
 size_t neogemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int c_col_major) {

@@ -102,6 +102,41 @@ def matmul(A: torch.Tensor, B: torch.Tensor, out: Optional[torch.Tensor] = None,
     return out
 
 
+ACTIVATIONS = {"none": 0, "relu": 1, "gelu_tanh": 2}
+
+
+def matmul_fused(A: torch.Tensor, B: torch.Tensor, out: Optional[torch.Tensor] = None,
+                 alpha: float = 1.0, beta: float = 0.0, bias: Optional[torch.Tensor] = None,
+                 activation: str = "none", col_major: bool = False) -> torch.Tensor:
+    """out = act(alpha * A @ B^T + beta * out + bias), in fp32 on the accumulator, rounded once.
+    ``bias`` is a bf16 vector of length N; ``out`` is required when beta != 0.  With
+    ``col_major`` the result is stored as neoGemmV1 stores it (``out`` is then [N,M])."""
+    M, N, K = _check_operands(A, B)
+    shape = (N, M) if col_major else (M, N)
+    if out is None:
+        if beta != 0.0:
+            raise ValueError("beta != 0 needs the tensor to accumulate into (out=)")
+        out = torch.empty(shape, dtype=torch.bfloat16, device=A.device)
+    else:
+        _require_cuda_bf16_matrix("out", out)
+        if tuple(out.shape) != shape or out.device != A.device:
+            raise ValueError(f"out must be {list(shape)} on {A.device}")
+    if bias is not None:
+        if (not bias.is_cuda or bias.dtype != torch.bfloat16 or bias.numel() != N
+                or not bias.is_contiguous()):
+            raise ValueError(f"bias must be a contiguous CUDA bfloat16 vector of length {N}")
+    if activation not in ACTIVATIONS:
+        raise ValueError(f"activation must be one of {sorted(ACTIVATIONS)}")
+    with torch.cuda.device(A.device):
+        rc = lib.neogemm_bf16_nt_fused(
+            A.data_ptr(), B.data_ptr(), out.data_ptr(), M, N, K, _row_pitch("A", A),
+            _row_pitch("B", B), _row_pitch("out", out), 1 if col_major else 0, float(alpha),
+            float(beta), None if bias is None else bias.data_ptr(), ACTIVATIONS[activation], None,
+            0, _stream_ptr(A.device))
+    check(rc)
+    return out
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     """y = x @ weight^T for x[..., K] and weight[N, K] (the layout of torch.nn.Linear): the
     operator's own layout is already x * W^T (benchmark.py:10-11,18)."""
@@ -163,5 +198,5 @@ def set_override(cta_group: int = -1, block_n: int = -1, swap: int = -1, stream_
     check(lib.neogemm_set_override(cta_group, block_n, swap, stream_k, group_m, max_ctas))
 
 
-__all__ = ["neoGemmV1", "neogemm", "matmul", "linear", "matmul_host", "workspace_bytes",
+__all__ = ["neoGemmV1", "neogemm", "matmul", "matmul_fused", "linear", "matmul_host", "workspace_bytes",
            "device_status", "clear_device_status", "last_config", "set_override", "NeoGemmError"]

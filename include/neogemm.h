@@ -67,6 +67,20 @@ int neogemm_bf16_nt(const void* A, const void* B, void* C,
                     void* workspace, size_t workspace_bytes,
                     void* stream);
 
+/* Fused epilogue:  C = act(alpha * A * B^T + beta * C + bias), computed in fp32 on the
+ * accumulator before the single rounding to bf16.
+ *   alpha, beta : fp32 scalars; with beta != 0 the previous contents of C are read (same layout)
+ *   bias        : NULL, or N bf16 values, bias[j] added to column j of C = A * B^T (the bias of a
+ *                 linear layer whose weight is B)
+ *   activation  : 0 none, 1 ReLU, 2 GELU (tanh form)
+ * Everything else as neogemm_bf16_nt(); K must be > 0.  The reference declares alpha and beta as
+ * kernel parameters and comments the intent but never implements it (neogemmv4.cu:166,266). */
+int neogemm_bf16_nt_fused(const void* A, const void* B, void* C,
+                          int64_t M, int64_t N, int64_t K,
+                          int64_t lda, int64_t ldb, int64_t ldc, int c_col_major,
+                          float alpha, float beta, const void* bias, int activation,
+                          void* workspace, size_t workspace_bytes, void* stream);
+
 /* The same product for callers that must not allocate: it calls no cudaMalloc, cudaFree,
  * cudaHostAlloc or any other allocating routine, on any call.  (No counterpart in the reference.)
  *
