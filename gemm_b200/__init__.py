@@ -8,7 +8,8 @@ without the library, so that it can create it.
 import importlib
 
 __all__ = ["neoGemmV1", "neogemm", "matmul", "matmul_fused", "linear", "matmul_host", "workspace_bytes",
-           "device_status", "clear_device_status", "last_config", "set_override", "NeoGemmError"]
+           "device_status", "clear_device_status", "last_config", "set_override", "set_tuning",
+           "NeoGemmError"]
 
 
 def __getattr__(name):

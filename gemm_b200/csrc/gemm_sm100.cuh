@@ -85,10 +85,16 @@ struct GemmParams {
   int* status;
 };
 
-template <int kCtaGroup_, int BLOCK_N_, int kStages_, int kEpiMode_>
+template <int kCtaGroup_, int BLOCK_N_, int kStages_, int kEpiMode_, int kNHalves_ = 1>
 struct GemmConfig {
   static constexpr int kCtaGroup = kCtaGroup_;
-  static constexpr int BLOCK_N = BLOCK_N_;           // UMMA N = tile columns
+  static constexpr int BLOCK_N = BLOCK_N_;           // UMMA N
+  // kNHalves == 2: the tile is two UMMA-N-wide halves side by side that share the X operand, each
+  // with its own TMEM accumulator (all 512 columns in use, so there is no second accumulator set:
+  // the next tile's main loop waits half by half for the epilogue to drain).  The point is fewer
+  // bytes into the SM per flop: X is fetched once for 2 x BLOCK_N columns.
+  static constexpr int kNHalves = kNHalves_;
+  static constexpr int TILE_N = BLOCK_N * kNHalves;  // tile columns
   static constexpr int kStages = kStages_;
   static constexpr int kEpiMode = kEpiMode_;
   static constexpr int BLOCK_M = 128;                 // rows of X (TMEM lanes) per CTA
@@ -97,25 +103,31 @@ struct GemmConfig {
   static constexpr int UMMA_K = 16;
   static constexpr int LOAD_N = BLOCK_N / kCtaGroup;  // rows of Y each CTA fetches
   static constexpr int SMEM_X = BLOCK_M * BLOCK_K * 2;
-  static constexpr int SMEM_Y = LOAD_N * BLOCK_K * 2;
+  static constexpr int SMEM_Y_HALF = LOAD_N * BLOCK_K * 2;
+  static constexpr int SMEM_Y = kNHalves * SMEM_Y_HALF;
   static constexpr int SMEM_STAGE = SMEM_X + SMEM_Y;
   static constexpr int EPI_COLS = 64;                 // columns per TMA-store box (128 B of bf16)
   static constexpr int SMEM_EPI_WARP_BUF = 32 * EPI_COLS * 2;  // 4 KB: 32 rows x 128 B
-  static constexpr int kEpiBufs = 2;
+  // One-half tiles: four epilogue warps, two staging buffers each.  Two-half tiles: eight
+  // epilogue warps (four per half, so both halves drain at once), one buffer each.
+  static constexpr int kEpiWarps = 4 * kNHalves;
+  static constexpr int kEpiBufs = (kNHalves == 1) ? 2 : 1;
   // Direct mode stages a warp's 32 rows x BLOCK_N columns transposed ([column][32 rows], 64 B per
   // column) so that a transposed result leaves as 16-byte vectors instead of 2-byte scalars.
   static constexpr int SMEM_EPI_T_WARP = BLOCK_N * 64;
-  static constexpr int SMEM_EPI = (kEpiMode == kEpiTmaStore) ? 4 * kEpiBufs * SMEM_EPI_WARP_BUF
+  static constexpr int SMEM_EPI = (kEpiMode == kEpiTmaStore) ? kEpiWarps * kEpiBufs * SMEM_EPI_WARP_BUF
                                                              : 4 * SMEM_EPI_T_WARP;
   static constexpr int SMEM_BARRIERS = (2 * kStages + 4) * 8 + 16;
   // +1024: the ring must start on a 1024-byte boundary for the 128-byte swizzle.
   static constexpr int SMEM_TOTAL = kStages * SMEM_STAGE + SMEM_EPI + SMEM_BARRIERS + 1024;
   static constexpr int kAccumCols = BLOCK_N;          // fp32 columns per accumulator
-  static constexpr int kTmemCols = (kCtaGroup == 2) ? 512
+  static constexpr int kTmemCols = (kCtaGroup == 2 || kNHalves == 2) ? 512
       : (2 * BLOCK_N <= 32) ? 32 : (2 * BLOCK_N <= 64) ? 64 : (2 * BLOCK_N <= 128) ? 128
       : (2 * BLOCK_N <= 256) ? 256 : 512;
-  static constexpr int kThreads = 192;
+  static constexpr int kThreads = 64 + 32 * kEpiWarps;   // TMA warp, MMA warp, epilogue warps
   static_assert(BLOCK_N % 16 == 0 && BLOCK_N >= 16 && BLOCK_N <= 256, "UMMA N");
+  static_assert(kNHalves == 1 || (kNHalves == 2 && BLOCK_N == 256 && kEpiMode == kEpiTmaStore),
+                "the two-half tile fills tensor memory: 2 x 256 fp32 columns, TMA-store epilogue");
   static_assert(SMEM_Y % 1024 == 0 || kStages == 1 || (SMEM_STAGE % 1024 == 0), "swizzle align");
   static_assert(SMEM_STAGE % 1024 == 0, "every stage must keep 1024-byte alignment");
   static_assert(kEpiMode == kEpiDirect || BLOCK_N % EPI_COLS == 0, "TMA-store boxes are 64 wide");
@@ -409,7 +421,8 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tmem_full_bar + 8 * a, 1);               // one tcgen05.commit per tile
-      mbar_init(tmem_empty_bar + 8 * a, 4 * kCtaGroup);  // one arrive per epilogue warp
+      // one arrive per epilogue warp that reads the accumulator (all of them for two-half tiles)
+      mbar_init(tmem_empty_bar + 8 * a, Cfg::kEpiWarps * kCtaGroup);
     }
     fence_barrier_init();
   }
@@ -456,7 +469,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
         int tm, tn;
         tile_coords(p, seg.tile, tm, tn);
         const int row_x = tm * Cfg::TILE_M + static_cast<int>(cta_rank) * Cfg::BLOCK_M;
-        const int row_y = tn * BLOCK_N + static_cast<int>(cta_rank) * Cfg::LOAD_N;
+        const int row_y = tn * Cfg::TILE_N + static_cast<int>(cta_rank) * Cfg::LOAD_N;
         const int kb_end = seg.kb_begin + seg.kb_count;
         for (int kb = seg.kb_begin; kb < kb_end; ++kb) {
           wait_timer.begin();
@@ -478,14 +491,24 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
               mbar_arrive_expect_tx(full_bar + 8 * stage, Cfg::SMEM_STAGE);
               if (hint_x) tma_load_2d_hint(sx, &tmap_x, full_bar + 8 * stage, c0, row_x, pol_x);
               else tma_load_2d(sx, &tmap_x, full_bar + 8 * stage, c0, row_x);
-              if (hint_y) tma_load_2d_hint(sy, &tmap_y, full_bar + 8 * stage, c0, row_y, pol_y);
-              else tma_load_2d(sy, &tmap_y, full_bar + 8 * stage, c0, row_y);
+#pragma unroll
+              for (int h = 0; h < Cfg::kNHalves; ++h) {
+                const uint32_t dst = sy + h * Cfg::SMEM_Y_HALF;
+                const int ry = row_y + h * BLOCK_N;
+                if (hint_y) tma_load_2d_hint(dst, &tmap_y, full_bar + 8 * stage, c0, ry, pol_y);
+                else tma_load_2d(dst, &tmap_y, full_bar + 8 * stage, c0, ry);
+              }
             } else {
               if (is_leader) mbar_arrive_expect_tx(full_bar + 8 * stage, 2 * Cfg::SMEM_STAGE);
               if (hint_x) tma_load_2d_pair_hint(sx, &tmap_x, leader_full + 8 * stage, c0, row_x, pol_x);
               else tma_load_2d_pair(sx, &tmap_x, leader_full + 8 * stage, c0, row_x);
-              if (hint_y) tma_load_2d_pair_hint(sy, &tmap_y, leader_full + 8 * stage, c0, row_y, pol_y);
-              else tma_load_2d_pair(sy, &tmap_y, leader_full + 8 * stage, c0, row_y);
+#pragma unroll
+              for (int h = 0; h < Cfg::kNHalves; ++h) {
+                const uint32_t dst = sy + h * Cfg::SMEM_Y_HALF;
+                const int ry = row_y + h * BLOCK_N;
+                if (hint_y) tma_load_2d_pair_hint(dst, &tmap_y, leader_full + 8 * stage, c0, ry, pol_y);
+                else tma_load_2d_pair(dst, &tmap_y, leader_full + 8 * stage, c0, ry);
+              }
             }
           }
           __syncwarp();
@@ -514,20 +537,85 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
       loop_timer.stamp(9);
       loop_timer.begin();
       while (ok && it.next(seg)) {
-        const uint32_t acc = seg_idx & 1, acc_phase = (seg_idx >> 1) & 1;
-        tmem_timer.begin();
-        const bool drained = __all_sync(
-            0xffffffffu,
-            mbar_wait<kCtaGroup == 2>(tmem_empty_bar + 8 * acc, acc_phase ^ 1, abort_flag));
-        tmem_timer.end();
-        if (!drained) {
-          if (lane == 0)
-            report_error(p, abort_flag, kDevTimeoutMmaTmem, seg_idx, static_cast<int>(acc));
-          break;
+        // One-half tiles alternate between two accumulators (two tiles in flight); a two-half
+        // tile owns both, and each half is waited for just before its first MMA.
+        const uint32_t acc = (Cfg::kNHalves == 1) ? (seg_idx & 1) : 0;
+        const uint32_t acc_phase = (Cfg::kNHalves == 1) ? ((seg_idx >> 1) & 1) : (seg_idx & 1);
+        if (Cfg::kNHalves == 1) {
+          tmem_timer.begin();
+          const bool drained = __all_sync(
+              0xffffffffu,
+              mbar_wait<kCtaGroup == 2>(tmem_empty_bar + 8 * acc, acc_phase ^ 1, abort_flag));
+          tmem_timer.end();
+          if (!drained) {
+            if (lane == 0)
+              report_error(p, abort_flag, kDevTimeoutMmaTmem, seg_idx, static_cast<int>(acc));
+            break;
+          }
+          tcgen05_fence_after();
         }
-        tcgen05_fence_after();
         const uint32_t tmem_d = tmem_base + acc * Cfg::kAccumCols;
-        for (int kb = 0; kb < seg.kb_count; ++kb) {
+        // Encoded distance between the two Y halves of a stage (16-byte units).
+        constexpr uint64_t kHalfStep = Cfg::SMEM_Y_HALF >> 4;
+        int kb_first = 0;
+        if (Cfg::kNHalves == 2) {
+          // Prologue of a two-half tile.  Half 0 comes back from the epilogue first, half 1 a
+          // little later, so the first k-blocks (as many as the ring holds minus one) are issued
+          // for half 0 alone, then, once half 1 is back, for half 1 - which also releases their
+          // ring slots.  The tensor pipe restarts as soon as half 0 is drained.
+          const int pro = min(kStages - 1, seg.kb_count);
+#pragma unroll 1
+          for (int h = 0; h < 2 && ok; ++h) {
+            tmem_timer.begin();
+            const bool drained = __all_sync(
+                0xffffffffu,
+                mbar_wait<kCtaGroup == 2>(tmem_empty_bar + 8 * h, acc_phase ^ 1, abort_flag));
+            tmem_timer.end();
+            if (!drained) {
+              if (lane == 0) report_error(p, abort_flag, kDevTimeoutMmaTmem, seg_idx, h);
+              ok = false;
+              break;
+            }
+            tcgen05_fence_after();
+            uint32_t st = stage, ph = phase;
+#pragma unroll 1
+            for (int j = 0; j < pro; ++j) {
+              if (h == 0) {
+                wait_timer.begin();
+                const bool got = __all_sync(
+                    0xffffffffu, mbar_wait(full_bar + 8 * st, ph, abort_flag,
+                                           static_cast<uint32_t>(p.main_wait_hint_ns)));
+                wait_timer.end();
+                if (!got) {
+                  if (lane == 0)
+                    report_error(p, abort_flag, kDevTimeoutMmaFull, seg_idx, static_cast<int>(st));
+                  ok = false;
+                  break;
+                }
+                tcgen05_fence_after();
+              }
+              const uint32_t sx = ring + st * Cfg::SMEM_STAGE;
+              const uint64_t desc_x = make_smem_desc_sw128(sx);
+              const uint64_t desc_y = make_smem_desc_sw128(sx + Cfg::SMEM_X) + h * kHalfStep;
+              if (elect_one()) {
+#pragma unroll
+                for (int k = 0; k < Cfg::BLOCK_K / Cfg::UMMA_K; ++k)
+                  umma_bf16<kCtaGroup>(tmem_d + h * Cfg::kAccumCols, desc_x + 2 * k, desc_y + 2 * k,
+                                       idesc, (j > 0 || k > 0) ? 1u : 0u);
+                if (h == 1) {
+                  if (kCtaGroup == 2) umma_commit_both_ctas(empty_bar + 8 * st);
+                  else umma_commit<1>(empty_bar + 8 * st);
+                }
+              }
+              __syncwarp();
+              if (++st == kStages) { st = 0; ph ^= 1; }
+            }
+            if (h == 1 && ok) { stage = st; phase = ph; }
+          }
+          if (!ok) break;
+          kb_first = pro;
+        }
+        for (int kb = kb_first; kb < seg.kb_count; ++kb) {
           wait_timer.begin();
           const bool got = __all_sync(0xffffffffu,
                                       mbar_wait(full_bar + 8 * stage, phase, abort_flag,
@@ -547,8 +635,11 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
 #pragma unroll
             for (int k = 0; k < Cfg::BLOCK_K / Cfg::UMMA_K; ++k) {
               // +32 bytes (two 16-byte units) per 16-element K step inside the swizzle row.
-              umma_bf16<kCtaGroup>(tmem_d, desc_x + 2 * k, desc_y + 2 * k, idesc,
-                                   (kb > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+              for (int h = 0; h < Cfg::kNHalves; ++h)
+                umma_bf16<kCtaGroup>(tmem_d + h * Cfg::kAccumCols, desc_x + 2 * k,
+                                     desc_y + h * kHalfStep + 2 * k, idesc,
+                                     (kb > 0 || k > 0) ? 1u : 0u);
             }
             if (kCtaGroup == 2) umma_commit_both_ctas(empty_bar + 8 * stage);
             else umma_commit<1>(empty_bar + 8 * stage);
@@ -575,6 +666,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
   } else {
     // ======================= epilogue (warps 2..5) =======================
     const uint32_t quad = warp & 3;               // TMEM lane quadrant this warp may read
+    const int warp_set = (warp - 2) >> 2;         // two-half tiles: which 128 columns of each half
     const int row_in_cta = quad * 32 + lane;      // accumulator row owned by this thread
     const uint32_t leader_tmem_empty = (kCtaGroup == 2) ? mapa_u32(tmem_empty_bar, 0) : 0u;
     SegmentIter it(p, worker, num_workers);
@@ -588,7 +680,8 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
     PhaseTimer wait_timer(timer_params), loop_timer(timer_params);
     loop_timer.begin();
     while (ok && it.next(seg)) {
-      const uint32_t acc = seg_idx & 1, acc_phase = (seg_idx >> 1) & 1;
+      const uint32_t acc = (Cfg::kNHalves == 1) ? (seg_idx & 1) : 0;
+      const uint32_t acc_phase = (Cfg::kNHalves == 1) ? ((seg_idx >> 1) & 1) : (seg_idx & 1);
       wait_timer.begin();
       // One lane polls; the other 31 sleep at the shuffle instead of hammering the barrier.
       int got_i = 0;
@@ -605,13 +698,13 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
       int tm, tn;
       tile_coords(p, seg.tile, tm, tn);
       const int row0 = tm * Cfg::TILE_M + static_cast<int>(cta_rank) * Cfg::BLOCK_M;
-      const int col0 = tn * BLOCK_N;
+      const int col0 = tn * Cfg::TILE_N;
       const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + acc * Cfg::kAccumCols;
 
       // ---- stream-K: publish this segment's partial; the last arriver finishes the rows ----
       bool finish = true;
       const float* tile_partials = nullptr;
-      {
+      if constexpr (Cfg::kNHalves == 1) {
         if (seg.n_contrib > 1) {
           // Slot layout [contributor][column][row] so that a warp's 32 rows of one column are
           // one 128-byte line.  Counters are per (tile, CTA of the pair, lane quadrant): the
@@ -657,22 +750,44 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
       }
 
       bool transposed = false;
+      bool released = false;
       if (!finish) {
         // nothing to store: another contributor completes these rows
       } else
       if (Cfg::kEpiMode == kEpiTmaStore) {
         const uint32_t warp_stage = epi_base + (warp - 2) * Cfg::kEpiBufs * Cfg::SMEM_EPI_WARP_BUF;
         const int my_row0 = row0 + quad * 32;
+        // One-half tiles: this warp walks all BLOCK_N columns.  Two-half tiles: the two sets of
+        // four warps split each half between them (128 columns = two boxes each) and do half 0
+        // first, so that half 0 goes back to the MMA warp after two boxes, half 1 after four.
+        constexpr int kBoxes = (Cfg::kNHalves == 1) ? BLOCK_N / Cfg::EPI_COLS : 4;
 #pragma unroll 1
-        for (int c = 0; c < BLOCK_N; c += Cfg::EPI_COLS) {
+        for (int i = 0; i < kBoxes; ++i) {
+          const int c = (Cfg::kNHalves == 1)
+              ? i * Cfg::EPI_COLS
+              : (i >> 1) * BLOCK_N + warp_set * (BLOCK_N / 2) + (i & 1) * Cfg::EPI_COLS;
+          const bool last_of_accumulator = (Cfg::kNHalves == 1) ? (i == kBoxes - 1) : ((i & 1) == 1);
           const uint32_t buf = warp_stage + (store_count % Cfg::kEpiBufs) * Cfg::SMEM_EPI_WARP_BUF;
-          // The store issued kEpiBufs boxes ago read from this buffer; make sure it is done.
-          if (lane == 0) tma_store_wait_read<Cfg::kEpiBufs - 1>();
-          __syncwarp();
           uint32_t r0[32], r1[32];
+          __syncwarp();
           tmem_ld_32x32b_x32(taddr + c, r0);
           tmem_ld_32x32b_x32(taddr + c + 32, r1);
           tmem_ld_wait();
+          if (last_of_accumulator) {
+            // This warp's last columns of the accumulator are in registers: hand it back now,
+            // before the conversion and the store of this box (one arrive per warp).
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+              const uint32_t which = (Cfg::kNHalves == 1) ? acc : static_cast<uint32_t>(i >> 1);
+              if (kCtaGroup == 2) mbar_arrive_cluster(leader_tmem_empty + 8 * which);
+              else mbar_arrive(tmem_empty_bar + 8 * which);
+            }
+            released = true;
+          }
+          // The store issued kEpiBufs boxes ago read from this buffer; make sure it is done.
+          if (lane == 0) tma_store_wait_read<Cfg::kEpiBufs - 1>();
+          __syncwarp();
           if (tile_partials != nullptr) {
             const float* base = tile_partials + static_cast<size_t>(c) * Cfg::TILE_M +
                                 cta_rank * Cfg::BLOCK_M + row_in_cta;
@@ -777,13 +892,17 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
         }
       }
 
-      // Accumulator drained: hand it back to the MMA warp (one arrive per warp).
+      // Accumulator drained: hand it back to the MMA warp (one arrive per warp), unless the
+      // store path already did so after its last tensor-memory load.
       __syncwarp();
       tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) {
-        if (kCtaGroup == 2) mbar_arrive_cluster(leader_tmem_empty + 8 * acc);
-        else mbar_arrive(tmem_empty_bar + 8 * acc);
+      if (lane == 0 && !released) {
+        // (only reached by paths that did not hand the accumulator back earlier; two-half tiles
+        // always do, in the store loop above)
+        const uint32_t which = acc;
+        if (kCtaGroup == 2) mbar_arrive_cluster(leader_tmem_empty + 8 * which);
+        else mbar_arrive(tmem_empty_bar + 8 * which);
       }
       if constexpr (Cfg::kEpiMode == kEpiDirect) {
         if (finish && transposed) {

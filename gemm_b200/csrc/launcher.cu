@@ -33,22 +33,25 @@ constexpr int kMaxDevices = 64;
 constexpr size_t kCounterRegionBytes = 256 * 1024;
 // Defaults of the neogemm_set_tuning keys: L2 hint mask, epilogue wait hint (ns), ring wait hint (ns).
 constexpr int kDefaultTuning[3] = {0, 2000, 0};
+// Throughput assumed for the 256 x 512 pair tile when ranking kernels (TFLOP/s at 8192^3).
+constexpr double kWideTileSpeed = 1650.0;
 
 // ------------------------------------------------------------------------------------------
 // Kernel table
 // ------------------------------------------------------------------------------------------
 struct KernelEntry {
-  int cta_group, block_n, stages, epi;
+  int cta_group, block_n, stages, epi, halves;
   const void* fn;
   int smem_bytes;
   int tmem_cols;
+  int threads;
 };
 
 template <class Cfg>
 KernelEntry make_entry() {
-  return KernelEntry{Cfg::kCtaGroup, Cfg::BLOCK_N, Cfg::kStages, Cfg::kEpiMode,
+  return KernelEntry{Cfg::kCtaGroup, Cfg::BLOCK_N, Cfg::kStages, Cfg::kEpiMode, Cfg::kNHalves,
                      reinterpret_cast<const void*>(&gemm_bf16_nt_kernel<Cfg>), Cfg::SMEM_TOTAL,
-                     Cfg::kTmemCols};
+                     Cfg::kTmemCols, Cfg::kThreads};
 }
 
 // Stage counts fill the 227 KB of shared memory; a CTA that owns more than half of it is alone on
@@ -57,6 +60,7 @@ const KernelEntry* kernel_table(int* count) {
   static const KernelEntry table[] = {
       make_entry<GemmConfig<1, 256, 4, kEpiTmaStore>>(),
       make_entry<GemmConfig<1, 128, 6, kEpiTmaStore>>(),
+      make_entry<GemmConfig<2, 256, 4, kEpiTmaStore, 2>>(),   // 256 x 512 tile, both accumulators
       make_entry<GemmConfig<2, 256, 6, kEpiTmaStore>>(),
       make_entry<GemmConfig<2, 128, 8, kEpiTmaStore>>(),
       make_entry<GemmConfig<1, 128, 6, kEpiDirect>>(),
@@ -68,11 +72,12 @@ const KernelEntry* kernel_table(int* count) {
   return table;
 }
 
-const KernelEntry* find_kernel(int cta_group, int block_n, int epi, int* index) {
+const KernelEntry* find_kernel(int cta_group, int block_n, int epi, int halves, int* index) {
   int n;
   const KernelEntry* t = kernel_table(&n);
   for (int i = 0; i < n; ++i) {
-    if (t[i].cta_group == cta_group && t[i].block_n == block_n && t[i].epi == epi) {
+    if (t[i].cta_group == cta_group && t[i].block_n == block_n && t[i].epi == epi &&
+        t[i].halves == halves) {
       if (index) *index = i;
       return &t[i];
     }
@@ -103,7 +108,7 @@ bool g_encode_looked_up = false;
 
 struct Override {
   int cta_group = -1, block_n = -1, swap = -1, stream_k = -1, group_m = -1, max_ctas = -1;
-  int tuning[3] = {-1, -1, -1};   // see neogemm_set_tuning
+  int tuning[4] = {-1, -1, -1, -1};   // see neogemm_set_tuning
 };
 thread_local Override t_override;
 thread_local int t_last_config[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -224,6 +229,7 @@ int get_tensor_map(const void* base, uint64_t inner, uint64_t rows, uint64_t pit
 struct Plan {
   bool swap = false;        // X = the operand that indexes output COLUMNS of the stored matrix
   int cta_group = 1, block_n = 256, epi = kEpiTmaStore;
+  int halves = 1;           // 2: 256 x 512 pair tile (two UMMA-N halves sharing X)
   bool stream_k = false;
   int sk_first_tile = 0;    // tiles below are handed out round-robin, tiles from here on are cut
   int sk_splits = 0;        // > 0: uniform k-chunks per cut tile (large kernels)
@@ -286,44 +292,57 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
     // Choose among the four TMA-store kernels by estimated time: waves of tiles over the
     // workers (SMs, or SM pairs) times the work of one tile per SM, divided by the throughput
     // each kernel reached at 8192^3 on a B200 (TFLOP/s, measured).  Overrides pin a field.
-    struct Candidate { int cta_group, block_n; double speed; };
-    const Candidate candidates[4] = {{2, 256, 1570.0}, {1, 256, 1430.0}, {1, 128, 1170.0},
-                                     {2, 128, 975.0}};
+    struct Candidate { int cta_group, block_n, halves; double speed; };
+    const Candidate candidates[5] = {{2, 256, 2, kWideTileSpeed}, {2, 256, 1, 1570.0},
+                                     {1, 256, 1, 1430.0}, {1, 128, 1, 1170.0}, {2, 128, 1, 975.0}};
     double best = 0.0;
-    int best_group = cta_group, best_n = block_n;
+    int best_group = cta_group, best_n = block_n, best_halves = 1;
+    const int wide = ov.tuning[3];   // -1 auto, 0 never, 1 always (when the shape allows)
     for (const Candidate& c : candidates) {
+      // An explicit tile-width override means the one-half kernels unless the wide tile is forced.
+      if (c.halves == 2 && (wide == 0 || ov.cta_group == 1 || (ov.block_n > 0 && wide != 1) ||
+                            (ov.block_n > 0 && ov.block_n != 256)))
+        continue;
+      if (c.halves == 1 && wide == 1 && nd > 256 && ov.cta_group != 1 &&
+          (ov.block_n < 0 || ov.block_n == 256))
+        continue;
       if (ov.cta_group > 0 && c.cta_group != ov.cta_group) continue;
       if (ov.block_n > 0 && c.block_n != ov.block_n) continue;
       if (c.block_n > block_n && ov.block_n < 0) continue;   // nd <= 128: no 256-wide tile
+      if (c.halves == 2 && nd <= 256) continue;
       const int64_t workers = std::max(1, sm_count / c.cta_group);
       const int64_t tm = 128 * c.cta_group;
-      const int64_t tiles = ((md + tm - 1) / tm) * ((nd + c.block_n - 1) / c.block_n);
+      const int64_t tile_n = static_cast<int64_t>(c.block_n) * c.halves;
+      const int64_t tiles = ((md + tm - 1) / tm) * ((nd + tile_n - 1) / tile_n);
       const int rest = static_cast<int>(tiles % workers);
       double waves = static_cast<double>(tiles / workers);
       if (rest > 0) {
-        const int cut = allow_hybrid && ov.stream_k != 0
+        const int cut = allow_hybrid && ov.stream_k != 0 && c.halves == 1
             ? hybrid_splits(rest, static_cast<int>(workers), static_cast<int>((K + 63) / 64)) : 0;
         waves += cut > 0 ? 1.0 / cut + 0.05 : 1.0;
       }
-      const double cost = waves * 128.0 * c.block_n / c.speed;
+      const double cost = waves * 128.0 * static_cast<double>(tile_n) / c.speed;
       if (best == 0.0 || cost < best) {
         best = cost;
         best_group = c.cta_group;
         best_n = c.block_n;
+        best_halves = c.halves;
       }
     }
     cta_group = best_group;
     block_n = best_n;
+    p.halves = best_halves;
   }
   p.block_n = block_n;
   p.cta_group = cta_group;
   p.epi = epi;
-  p.kernel = find_kernel(cta_group, block_n, epi, &p.kernel_index);
+  p.kernel = find_kernel(cta_group, block_n, epi, p.halves, &p.kernel_index);
   if (p.kernel == nullptr) return NEOGEMM_ERR_UNSUPPORTED;
 
   const int tile_m = 128 * cta_group;
   p.num_m_tiles = static_cast<int>((md + tile_m - 1) / tile_m);
-  p.num_n_tiles = static_cast<int>((nd + block_n - 1) / block_n);
+  const int tile_n = block_n * p.halves;
+  p.num_n_tiles = static_cast<int>((nd + tile_n - 1) / tile_n);
   const int64_t tiles = static_cast<int64_t>(p.num_m_tiles) * p.num_n_tiles;
   if (tiles > 0x3fffffffll) return NEOGEMM_ERR_UNSUPPORTED;
   p.num_tiles = static_cast<int>(tiles);
@@ -351,7 +370,8 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
     if (ov.stream_k >= 0) stream_k = (ov.stream_k != 0);
   } else {
     const int rest = p.num_tiles % workers;
-    sk_splits = allow_hybrid && ov.stream_k != 0 ? hybrid_splits(rest, workers, p.num_k_blocks) : 0;
+    sk_splits = allow_hybrid && ov.stream_k != 0 && p.halves == 1
+        ? hybrid_splits(rest, workers, p.num_k_blocks) : 0;
     stream_k = sk_splits > 0;
     sk_first = p.num_tiles - rest;
   }
@@ -434,7 +454,7 @@ int launch(DeviceState* st, const Plan& plan, const CUtensorMap& mx, const CUten
   cudaLaunchConfig_t cfg;
   std::memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(static_cast<unsigned>(plan.num_ctas), 1, 1);
-  cfg.blockDim = dim3(192, 1, 1);
+  cfg.blockDim = dim3(static_cast<unsigned>(k->threads), 1, 1);
   cfg.dynamicSmemBytes = static_cast<size_t>(k->smem_bytes);
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -578,7 +598,7 @@ int gemm_device(const void* A, const void* B, void* C, int64_t M, int64_t N, int
   }
 
   t_last_config[0] = plan.cta_group;
-  t_last_config[1] = plan.block_n;
+  t_last_config[1] = plan.block_n * plan.halves;
   t_last_config[2] = plan.kernel->stages;
   t_last_config[3] = plan.swap ? 1 : 0;
   t_last_config[4] = plan.stream_k ? 1 : 0;
@@ -770,7 +790,8 @@ int neogemm_set_phase_timers(void* device_buffer, size_t bytes) {
 }
 
 int neogemm_set_tuning(int key, int value) {
-  if (key < 0 || key > 2 || value > 1000000 || (key == 0 && value > 7)) return NEOGEMM_ERR_BAD_ARG;
+  if (key < 0 || key > 3 || value > 1000000 || (key == 0 && value > 7) || (key == 3 && value > 1))
+    return NEOGEMM_ERR_BAD_ARG;
   t_override.tuning[key] = value;
   return NEOGEMM_OK;
 }
@@ -786,7 +807,7 @@ int neogemm_debug_plan(int64_t M, int64_t N, int64_t K, int64_t ldc, int c_col_m
   const int64_t pn = c_col_major ? M : N;
   const int rc = make_plan(pm, pn, K, ldc, nullptr, sm_count, t_override, &plan);
   if (rc != NEOGEMM_OK) return -rc;
-  const int fields[16] = {plan.cta_group, plan.block_n, plan.kernel->stages, plan.swap ? 1 : 0,
+  const int fields[16] = {plan.cta_group, plan.block_n * plan.halves, plan.kernel->stages, plan.swap ? 1 : 0,
                           plan.stream_k ? 1 : 0, plan.num_ctas, plan.num_tiles, plan.group_m,
                           plan.epi, plan.Md, plan.Nd, plan.num_m_tiles, plan.num_n_tiles,
                           plan.num_k_blocks, plan.max_contrib, plan.sk_first_tile};

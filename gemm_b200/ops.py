@@ -198,5 +198,14 @@ def set_override(cta_group: int = -1, block_n: int = -1, swap: int = -1, stream_
     check(lib.neogemm_set_override(cta_group, block_n, swap, stream_k, group_m, max_ctas))
 
 
+TUNING_KEYS = {"l2_hints": 0, "epilogue_wait_hint_ns": 1, "ring_wait_hint_ns": 2, "wide_tile": 3}
+
+
+def set_tuning(key: str, value: int = -1) -> None:
+    """Set one tuning knob on this thread (-1 = library default); keys: TUNING_KEYS."""
+    check(lib.neogemm_set_tuning(TUNING_KEYS[key], int(value)))
+
+
 __all__ = ["neoGemmV1", "neogemm", "matmul", "matmul_fused", "linear", "matmul_host", "workspace_bytes",
-           "device_status", "clear_device_status", "last_config", "set_override", "NeoGemmError"]
+           "device_status", "clear_device_status", "last_config", "set_override", "set_tuning",
+           "NeoGemmError"]

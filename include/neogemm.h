@@ -158,6 +158,8 @@ int neogemm_set_override(int cta_group, int block_n, int swap, int stream_k, int
  *   key 1: nanoseconds the epilogue warps may stay suspended in one mbarrier.try_wait while they
  *          wait for a finished accumulator (0 = plain try_wait).
  *   key 2: the same for the TMA producer's and the MMA warp's waits on the operand ring.
+ *   key 3: the 256 x 512 pair tile (two UMMA-N halves sharing one operand): 0 never, 1 whenever
+ *          the shape allows, -1 chosen by estimated time.
  * No counterpart in the reference (its maps only set L2 promotion, nemgemmV03.cu:52). */
 int neogemm_set_tuning(int key, int value);
 

@@ -64,3 +64,39 @@ def test_cut_last_wave_is_chosen_for_4096_cube_and_is_deterministic():
         assert torch.equal(first.view(torch.int16), ops.matmul(dA, dB).view(torch.int16))
     torch.cuda.synchronize()
     assert ops.device_status()[0] == 0
+
+
+def test_wide_pair_tile_is_the_default_for_8192_cube():
+    stats, cfg = run_case(8192, 8192, 8192)
+    assert (cfg["cta_group"], cfg["block_n"], cfg["stages"]) == (2, 512, 4), cfg
+
+
+@pytest.mark.parametrize("shape", [(512, 1024, 512), (520, 776, 1352), (130, 264, 72),
+                                   (1000, 1544, 200), (4096, 4096, 1024)])
+def test_wide_pair_tile_ragged(shape):
+    # 256 x 512 tile: both TMEM accumulators belong to one tile; ragged rows, columns and K,
+    # a second half that is partly or wholly out of range, several tiles per CTA pair.
+    stats, cfg = run_case(*shape, tuning={"wide_tile": 1})
+    assert cfg["block_n"] == 512 and cfg["cta_group"] == 2, cfg
+    run_case(*shape, tuning={"wide_tile": 1}, col_major=True)
+
+
+def test_wide_pair_tile_is_deterministic_and_never_wide_when_switched_off():
+    from gemm_b200.inputs import make_problem
+    A, B = make_problem(2048, 4096, 1024, seed=14)
+    dA, dB = A.cuda(), B.cuda()
+    ops.set_tuning("wide_tile", 1)
+    try:
+        first = ops.matmul(dA, dB).clone()
+        assert ops.last_config()["block_n"] == 512
+        for _ in range(10):
+            assert torch.equal(first.view(torch.int16), ops.matmul(dA, dB).view(torch.int16))
+        ops.set_tuning("wide_tile", 0)
+        other = ops.matmul(dA, dB)
+        assert ops.last_config()["block_n"] <= 256
+    finally:
+        ops.set_tuning("wide_tile", -1)
+    torch.cuda.synchronize()
+    assert ops.device_status()[0] == 0
+    # same k order per element in both kernels -> identical bits
+    assert torch.equal(first.view(torch.int16), other.view(torch.int16))

@@ -7,7 +7,7 @@ from oracle import oracle
 
 
 def run_case(M, N, K, col_major=False, seed=1234, override=None, scale_by_k=True, what=None,
-             expect=None, **gates):
+             expect=None, tuning=None, **gates):
     """One parity case through the C ABI: seeded operands -> GPU kernel -> compare with oracle.
     The output is poisoned with NaN first so unwritten elements cannot pass."""
     A, B = make_problem(M, N, K, seed=seed, scale_by_k=scale_by_k)
@@ -15,6 +15,8 @@ def run_case(M, N, K, col_major=False, seed=1234, override=None, scale_by_k=True
     try:
         if override:
             ops.set_override(**override)
+        for key, value in (tuning or {}).items():
+            ops.set_tuning(key, value)
         if col_major:
             C = torch.full((N, M), float("nan"), dtype=torch.bfloat16, device="cuda")
             ops.neoGemmV1(dA, dB, C)
@@ -27,6 +29,8 @@ def run_case(M, N, K, col_major=False, seed=1234, override=None, scale_by_k=True
     finally:
         if override:
             ops.set_override()
+        for key in (tuning or {}):
+            ops.set_tuning(key, -1)
     torch.cuda.synchronize()
     status = ops.device_status()
     assert status[0] == 0, f"device reported {status} for {M}x{N}x{K} cfg={cfg}"
