@@ -45,6 +45,7 @@ enum DeviceError : int {
   kDevTimeoutEpilogue = 4,   // epilogue gave up waiting for a finished accumulator
   kDevTmemAddress = 5,       // tensor-memory allocation did not start at column 0 (pair mode)
   kDevBounds = 6,            // an index left its buffer (access skipped); aux: 1 partials, 2 counters, 3 C
+  kDevTimeoutScheduler = 7,  // a role gave up waiting on the dynamic-claim queue
 };
 
 struct GemmParams {
@@ -66,6 +67,13 @@ struct GemmParams {
                              // one per worker (worker w takes chunk w / tiles of tile w % tiles),
                              // instead of one contiguous unit range per worker
   int max_contrib;           // partial slots per tile in `partials`
+  // Dynamic tail pool (pure stream-K only; all zero otherwise).  The last dyn_ppt * dyn_piece_kb
+  // k-blocks of every tile are not part of any CTA's static range: they form dyn_pieces fixed
+  // pieces that CTAs claim from `dyn_counter` as they run out of static work, which evens out
+  // the uneven HBM service the SMs get.  Pieces are fixed (tile, k-range) units with their own
+  // partial slot, so the result does not depend on who computed which piece.
+  int dyn_pieces, dyn_ppt, dyn_piece_kb, dyn_static_kb;
+  int* dyn_counter;          // zero before launch; the launch's last claim re-zeroes it
   float* partials;           // [stream-K tiles][max_contrib][BLOCK_N][TILE_M] fp32
   int* tile_counters;        // [stream-K tiles][kCtaGroup][4], zero before launch; the last arriver
                              // of each entry re-zeroes it
@@ -117,7 +125,7 @@ struct GemmConfig {
   static constexpr int SMEM_EPI_T_WARP = BLOCK_N * 64;
   static constexpr int SMEM_EPI = (kEpiMode == kEpiTmaStore) ? kEpiWarps * kEpiBufs * SMEM_EPI_WARP_BUF
                                                              : 4 * SMEM_EPI_T_WARP;
-  static constexpr int SMEM_BARRIERS = (2 * kStages + 4) * 8 + 16;
+  static constexpr int SMEM_BARRIERS = (2 * kStages + 8) * 8 + 16;
   // +1024: the ring must start on a 1024-byte boundary for the 128-byte swizzle.
   static constexpr int SMEM_TOTAL = kStages * SMEM_STAGE + SMEM_EPI + SMEM_BARRIERS + 1024;
   static constexpr int kAccumCols = BLOCK_N;          // fp32 columns per accumulator
@@ -148,7 +156,7 @@ struct Segment {
 
 // Enumerates this CTA's segments.  Every role constructs one and walks the same sequence.
 struct SegmentIter {
-  int num_k_blocks;
+  int num_k_blocks, real_k_blocks, dyn_ppt, dyn_piece_kb;
   // round-robin part: tiles [0, dp_tiles)
   int next_tile, tile_step, dp_tiles;
   // stream-K part: tiles [sk_first, sk_first + sk_tiles); this CTA's unit range [u0, u1) is cut
@@ -158,14 +166,19 @@ struct SegmentIter {
   int num_ctas, phase, splits, worker_id;
 
   __host__ __device__ __forceinline__ SegmentIter(const GemmParams& p, int worker, int num_workers) {
-    num_k_blocks = p.num_k_blocks;
+    // With a dynamic tail pool the static ranges only cover the first dyn_static_kb k-blocks of
+    // every tile; `num_k_blocks` is the per-tile length of that static unit space.
+    dyn_ppt = p.dyn_pieces > 0 ? p.dyn_ppt : 0;
+    dyn_piece_kb = p.dyn_piece_kb;
+    real_k_blocks = p.num_k_blocks;
+    num_k_blocks = dyn_ppt > 0 ? p.dyn_static_kb : p.num_k_blocks;
     next_tile = worker;
     tile_step = num_workers;
     num_ctas = num_workers;
     sk_first = p.stream_k ? p.sk_first_tile : p.num_tiles;
     sk_tiles = p.num_tiles - sk_first;
     dp_tiles = sk_first;
-    total_units = static_cast<long long>(sk_tiles) * p.num_k_blocks;
+    total_units = static_cast<long long>(sk_tiles) * num_k_blocks;
     phase = sk_tiles > 0 ? 0 : 3;
     splits = p.stream_k ? p.sk_splits : 0;
     worker_id = worker;
@@ -203,13 +216,29 @@ struct SegmentIter {
     s.kb_count = static_cast<int>(b - a);
     if (s.kb_count == num_k_blocks) {
       s.contrib = 0;
-      s.n_contrib = 1;
+      s.n_contrib = 1 + dyn_ppt;
     } else {
       const int first = owner_of(tile_u0);
       const int last = owner_of(tile_u0 + num_k_blocks - 1);
       s.contrib = owner_of(a) - first;
-      s.n_contrib = last - first + 1;
+      s.n_contrib = last - first + 1 + dyn_ppt;
     }
+  }
+
+  // Segment of dynamic piece `id`: piece j of tile slot id / dyn_ppt, after that tile's static
+  // contributors in the summation order.
+  __host__ __device__ __forceinline__ void piece(Segment& s, int id) const {
+    const int slot = id / dyn_ppt;
+    const int j = id - slot * dyn_ppt;
+    const long long tile_u0 = static_cast<long long>(slot) * num_k_blocks;
+    const int n_static = owner_of(tile_u0 + num_k_blocks - 1) - owner_of(tile_u0) + 1;
+    s.tile = sk_first + slot;
+    s.sk_slot = slot;
+    s.kb_begin = num_k_blocks + j * dyn_piece_kb;
+    const int left = real_k_blocks - s.kb_begin;
+    s.kb_count = left < dyn_piece_kb ? left : dyn_piece_kb;
+    s.contrib = n_static + j;
+    s.n_contrib = n_static + dyn_ppt;
   }
 
   // Order: the stream-K share first (its two partial segments, then its whole tiles), the
@@ -319,6 +348,68 @@ __device__ __forceinline__ void report_error(const GemmParams& p, volatile int* 
   }
 }
 
+// Where a role gets its segments from: first the static sequence every role derives on its own
+// (SegmentIter), then - if the launch has a dynamic tail pool - pieces claimed at run time.  The
+// TMA warp claims (atomicAdd on a global counter) and publishes each claim to the MMA warp and
+// the four epilogue warps through a two-slot queue in shared memory guarded by mbarriers; -1
+// ends the stream.  Waits are bounded like every other wait in the kernel.
+struct WorkSource {
+  SegmentIter it;
+  uint32_t sched_full, sched_empty;   // [2] each
+  volatile int* ids;                  // [2]
+  const volatile int* abort_flag;
+  uint32_t q, qphase;
+  bool is_claimer, done, failed;
+  int dyn_pieces, num_workers;
+  int* dyn_counter;
+
+  __device__ __forceinline__ WorkSource(const GemmParams& p, int worker, int workers, bool claimer,
+                                        uint32_t full_bar, uint32_t empty_bar, volatile int* ids_,
+                                        const volatile int* abort)
+      : it(p, worker, workers), sched_full(full_bar), sched_empty(empty_bar), ids(ids_),
+        abort_flag(abort), q(0), qphase(0), is_claimer(claimer), done(p.dyn_pieces == 0),
+        failed(false), dyn_pieces(p.dyn_pieces), num_workers(workers), dyn_counter(p.dyn_counter) {}
+
+  // Warp-collective: all 32 lanes call it together and get the same answer.
+  __device__ __forceinline__ bool next(Segment& s, uint32_t lane) {
+    if (it.next(s)) return true;
+    if (done) return false;
+    int id = -1;
+    if (is_claimer) {
+      if (!__all_sync(0xffffffffu, ptx::mbar_wait(sched_empty + 8 * q, qphase ^ 1, abort_flag))) {
+        failed = done = true;
+        return false;
+      }
+      if (lane == 0) {
+        const int got = atomicAdd(dyn_counter, 1);
+        // Every CTA claims until it draws an id past the end, exactly once: the launch makes
+        // dyn_pieces + num_workers claims in total, and the last one resets the counter.
+        if (got == dyn_pieces + num_workers - 1) *dyn_counter = 0;
+        id = got < dyn_pieces ? got : -1;
+        ids[q] = id;
+        ptx::mbar_arrive(sched_full + 8 * q);   // release: publishes ids[q]
+      }
+      id = __shfl_sync(0xffffffffu, id, 0);
+    } else {
+      if (!__all_sync(0xffffffffu, ptx::mbar_wait(sched_full + 8 * q, qphase, abort_flag))) {
+        failed = done = true;
+        return false;
+      }
+      id = ids[q];
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(sched_empty + 8 * q);
+    }
+    q ^= 1;
+    if (q == 0) qphase ^= 1;
+    if (id < 0) {
+      done = true;
+      return false;
+    }
+    it.piece(s, id);
+    return true;
+  }
+};
+
 // Fused epilogue on kN consecutive columns [col, col + kN) of one row of D held in r[] (fp32
 // bit patterns), in place.  Reads of C_in and bias are bounds-checked against Md / Nd.
 template <int kN>
@@ -357,21 +448,33 @@ template <int kN>
 __device__ __forceinline__ void sum_partials(uint32_t (&r)[kN], const float* col_base,
                                              size_t col_stride, size_t slot_stride, int contrib,
                                              int n_contrib) {
+  // Up to kGroup contributors' loads are issued before any is consumed (kGroup * kN independent
+  // loads in flight per thread, each a 128-byte line per warp), then added in contributor order.
+  constexpr int kGroup = (kN <= 16) ? 4 : 2;
   float sum[kN];
 #pragma unroll 1
-  for (int q = 0; q < n_contrib; ++q) {
-    float t[kN];
-    if (q == contrib) {
+  for (int q0 = 0; q0 < n_contrib; q0 += kGroup) {
+    float t[kGroup][kN];
 #pragma unroll
-      for (int j = 0; j < kN; ++j) t[j] = __uint_as_float(r[j]);
-    } else {
-      // kN independent loads in flight per thread (one 128-byte line per warp each).
-      const float* src = col_base + static_cast<size_t>(q) * slot_stride;
+    for (int g = 0; g < kGroup; ++g) {
+      const int q = q0 + g;
+      if (q < n_contrib && q != contrib) {
+        const float* src = col_base + static_cast<size_t>(q) * slot_stride;
 #pragma unroll
-      for (int j = 0; j < kN; ++j) t[j] = __ldcg(src + static_cast<size_t>(j) * col_stride);
+        for (int j = 0; j < kN; ++j) t[g][j] = __ldcg(src + static_cast<size_t>(j) * col_stride);
+      }
     }
 #pragma unroll
-    for (int j = 0; j < kN; ++j) sum[j] = (q == 0) ? t[j] : sum[j] + t[j];
+    for (int g = 0; g < kGroup; ++g) {
+      const int q = q0 + g;
+      if (q < n_contrib) {
+#pragma unroll
+        for (int j = 0; j < kN; ++j) {
+          const float v = (q == contrib) ? __uint_as_float(r[j]) : t[g][j];
+          sum[j] = (q == 0) ? v : sum[j] + v;
+        }
+      }
+    }
   }
 #pragma unroll
   for (int j = 0; j < kN; ++j) r[j] = __float_as_uint(sum[j]);
@@ -399,10 +502,13 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
   const uint32_t empty_bar = full_bar + 8 * kStages;        // [kStages]
   const uint32_t tmem_full_bar = empty_bar + 8 * kStages;   // [2]
   const uint32_t tmem_empty_bar = tmem_full_bar + 16;       // [2]
-  const uint32_t tmem_slot = tmem_empty_bar + 16;           // u32
+  const uint32_t sched_full_bar = tmem_empty_bar + 16;      // [2] dynamic-claim queue
+  const uint32_t sched_empty_bar = sched_full_bar + 16;     // [2]
+  const uint32_t tmem_slot = sched_empty_bar + 16;          // u32
   uint8_t* tail_gen = smem_gen + (tmem_slot - smem_base);
   volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(tail_gen);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tail_gen + 4);
+  volatile int* sched_ids = reinterpret_cast<volatile int*>(tail_gen + 8);   // [2]
 
   const int warp = threadIdx.x >> 5;
   const uint32_t lane = lane_id();
@@ -423,6 +529,8 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
       mbar_init(tmem_full_bar + 8 * a, 1);               // one tcgen05.commit per tile
       // one arrive per epilogue warp that reads the accumulator (all of them for two-half tiles)
       mbar_init(tmem_empty_bar + 8 * a, Cfg::kEpiWarps * kCtaGroup);
+      mbar_init(sched_full_bar + 8 * a, 1);                   // the claiming lane
+      mbar_init(sched_empty_bar + 8 * a, 1 + Cfg::kEpiWarps); // MMA warp + epilogue warps
     }
     fence_barrier_init();
   }
@@ -451,7 +559,8 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
     // The whole warp walks the loop so that every loop-carried value stays warp-uniform; one
     // elected lane issues the copies.
     if (*abort_flag == 0) {
-      SegmentIter it(p, worker, num_workers);
+      WorkSource it(p, worker, num_workers, true, sched_full_bar, sched_empty_bar, sched_ids,
+                    abort_flag);
       Segment seg;
       uint32_t stage = 0, phase = 0;
       int seg_idx = 0;
@@ -465,7 +574,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
       if (lane != 0) timer_params.timers = nullptr;
       PhaseTimer wait_timer(timer_params), loop_timer(timer_params);
       loop_timer.begin();
-      while (ok && it.next(seg)) {
+      while (ok && it.next(seg, lane)) {
         int tm, tn;
         tile_coords(p, seg.tile, tm, tn);
         const int row_x = tm * Cfg::TILE_M + static_cast<int>(cta_rank) * Cfg::BLOCK_M;
@@ -516,6 +625,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
         }
         ++seg_idx;
       }
+      if (it.failed && lane == 0) report_error(p, abort_flag, kDevTimeoutScheduler, seg_idx, 0);
       loop_timer.end();
       loop_timer.flush(1);
       wait_timer.flush(0);
@@ -525,7 +635,8 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
     // ======================= UMMA issuer (leader CTA only) =======================
     // Warp-uniform loop, one elected lane issues tcgen05.mma / tcgen05.commit.
     if (is_leader && *abort_flag == 0) {
-      SegmentIter it(p, worker, num_workers);
+      WorkSource it(p, worker, num_workers, false, sched_full_bar, sched_empty_bar, sched_ids,
+                    abort_flag);
       Segment seg;
       uint32_t stage = 0, phase = 0;
       int seg_idx = 0;
@@ -536,7 +647,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
       PhaseTimer wait_timer(timer_params), tmem_timer(timer_params), loop_timer(timer_params);
       loop_timer.stamp(9);
       loop_timer.begin();
-      while (ok && it.next(seg)) {
+      while (ok && it.next(seg, lane)) {
         // One-half tiles alternate between two accumulators (two tiles in flight); a two-half
         // tile owns both, and each half is waited for just before its first MMA.
         const uint32_t acc = (Cfg::kNHalves == 1) ? (seg_idx & 1) : 0;
@@ -655,6 +766,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
         __syncwarp();
         ++seg_idx;
       }
+      if (it.failed && lane == 0) report_error(p, abort_flag, kDevTimeoutScheduler, seg_idx, 1);
       loop_timer.end();
       loop_timer.stamp(10);
       loop_timer.flush(4);
@@ -669,7 +781,8 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
     const int warp_set = (warp - 2) >> 2;         // two-half tiles: which 128 columns of each half
     const int row_in_cta = quad * 32 + lane;      // accumulator row owned by this thread
     const uint32_t leader_tmem_empty = (kCtaGroup == 2) ? mapa_u32(tmem_empty_bar, 0) : 0u;
-    SegmentIter it(p, worker, num_workers);
+    WorkSource it(p, worker, num_workers, false, sched_full_bar, sched_empty_bar, sched_ids,
+                  abort_flag);
     Segment seg;
     int seg_idx = 0;
     uint32_t store_count = 0;
@@ -679,7 +792,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
     if (warp != 2 || lane != 0) timer_params.timers = nullptr;
     PhaseTimer wait_timer(timer_params), loop_timer(timer_params);
     loop_timer.begin();
-    while (ok && it.next(seg)) {
+    while (ok && it.next(seg, lane)) {
       const uint32_t acc = (Cfg::kNHalves == 1) ? (seg_idx & 1) : 0;
       const uint32_t acc_phase = (Cfg::kNHalves == 1) ? ((seg_idx >> 1) & 1) : (seg_idx & 1);
       wait_timer.begin();
@@ -735,17 +848,22 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
             for (int j = 0; j < 16; ++j)
               __stcg(mine + static_cast<size_t>(c + j) * Cfg::TILE_M, __uint_as_float(r[j]));
           }
-          __threadfence();
+          // Release: the warp's stores are ordered before lane 0's fence by the warp barrier, and
+          // the fence orders them before the counter increment for every other CTA (cumulativity),
+          // so one lane fences instead of thirty-two.  Acquire on the way back, same shape.
           __syncwarp();
           int* counter = p.tile_counters + counter_idx;
           int prev = 0;
-          if (lane == 0) prev = atomicAdd(counter, 1);
+          if (lane == 0) {
+            __threadfence();
+            prev = atomicAdd(counter, 1);
+            if (prev == seg.n_contrib - 1) {
+              __threadfence();
+              *counter = 0;  // ready for the next launch that uses this workspace
+            }
+          }
           prev = __shfl_sync(0xffffffffu, prev, 0);
           finish = (prev == seg.n_contrib - 1);
-          if (finish) {
-            __threadfence();
-            if (lane == 0) *counter = 0;  // ready for the next launch that uses this workspace
-          }
         }
       }
 
@@ -934,6 +1052,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
       }
       ++seg_idx;
     }
+    if (it.failed && lane == 0) report_error(p, abort_flag, kDevTimeoutScheduler, seg_idx, 2);
     if (Cfg::kEpiMode == kEpiTmaStore && lane == 0) tma_store_wait_all<0>();
     loop_timer.end();
     loop_timer.stamp(11);

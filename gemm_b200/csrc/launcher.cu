@@ -35,6 +35,10 @@ constexpr size_t kCounterRegionBytes = 256 * 1024;
 constexpr int kDefaultTuning[3] = {0, 2000, 0};
 // Throughput assumed for the 256 x 512 pair tile when ranking kernels (TFLOP/s at 8192^3).
 constexpr double kWideTileSpeed = 1650.0;
+// k-blocks per dynamically claimed piece of the stream-K tail pool.
+constexpr int kDynPieceKBlocks = 16;
+// Pieces per tile left to the pool unless tuning key 4 says otherwise.
+constexpr int kDefaultDynPieces = 1;
 
 // ------------------------------------------------------------------------------------------
 // Kernel table
@@ -108,7 +112,7 @@ bool g_encode_looked_up = false;
 
 struct Override {
   int cta_group = -1, block_n = -1, swap = -1, stream_k = -1, group_m = -1, max_ctas = -1;
-  int tuning[4] = {-1, -1, -1, -1};   // see neogemm_set_tuning
+  int tuning[5] = {-1, -1, -1, -1, -1};   // see neogemm_set_tuning
 };
 thread_local Override t_override;
 thread_local int t_last_config[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -233,6 +237,7 @@ struct Plan {
   bool stream_k = false;
   int sk_first_tile = 0;    // tiles below are handed out round-robin, tiles from here on are cut
   int sk_splits = 0;        // > 0: uniform k-chunks per cut tile (large kernels)
+  int dyn_ppt = 0, dyn_piece_kb = 0, dyn_static_kb = 0, dyn_pieces = 0;   // dynamic tail pool
   int group_m = 8;
   int num_ctas = 0;
   int Md = 0, Nd = 0;
@@ -377,7 +382,7 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
   }
   const int sk_tiles = stream_k ? p.num_tiles - sk_first : 0;
   if (stream_k &&
-      static_cast<size_t>(sk_tiles) * cta_group * 4 * sizeof(int) > kCounterRegionBytes) {
+      (static_cast<size_t>(sk_tiles) * cta_group * 4 + 1) * sizeof(int) > kCounterRegionBytes) {
     if (ov.stream_k > 0) return NEOGEMM_ERR_UNSUPPORTED;
     stream_k = false;
   }
@@ -385,13 +390,27 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
   p.sk_first_tile = stream_k ? sk_first : 0;
   p.sk_splits = stream_k ? sk_splits : 0;
   if (stream_k) {
-    const int64_t units = static_cast<int64_t>(sk_tiles) * p.num_k_blocks;
     if (sk_splits > 0) {
       p.max_contrib = sk_splits;
     } else {
-      workers = static_cast<int>(std::min<int64_t>(workers, units));
-      const int64_t per = std::max<int64_t>(1, units / workers);
-      p.max_contrib = static_cast<int>((p.num_k_blocks + per - 1) / per) + 1;
+      // Dynamic tail pool: with enough K, the last 16 or 32 k-blocks of every tile are left out
+      // of the static ranges and claimed at run time in pieces of 16 (tuning key 4: 0 = off).
+      int static_kb = p.num_k_blocks;
+      // Measured on the decode shapes: one piece per tile pays for 16 and 32 output columns
+      // (2 % faster at M=16); for wider tiles the extra partial round trips cost more than the
+      // balancing gains.
+      const int want = ov.tuning[4] >= 0 ? ov.tuning[4] : (block_n <= 32 ? kDefaultDynPieces : 0);
+      if (want > 0 && p.num_k_blocks >= 64 && cta_group == 1 && allow_hybrid) {
+        p.dyn_ppt = std::min(want, 4);
+        p.dyn_piece_kb = kDynPieceKBlocks;
+        p.dyn_static_kb = p.num_k_blocks - p.dyn_ppt * kDynPieceKBlocks;
+        p.dyn_pieces = sk_tiles * p.dyn_ppt;
+        static_kb = p.dyn_static_kb;
+      }
+      const int64_t static_units = static_cast<int64_t>(sk_tiles) * static_kb;
+      workers = static_cast<int>(std::min<int64_t>(workers, static_units));
+      const int64_t per = std::max<int64_t>(1, static_units / workers);
+      p.max_contrib = static_cast<int>((static_kb + per - 1) / per) + 1 + p.dyn_ppt;
     }
     // The arrival counters always occupy the same fixed region at the start of a workspace, so
     // that launches of different shapes sharing one workspace never see each other's partials
@@ -559,6 +578,10 @@ int gemm_device(const void* A, const void* B, void* C, int64_t M, int64_t N, int
   params.stream_k = plan.stream_k ? 1 : 0;
   params.sk_first_tile = plan.sk_first_tile;
   params.sk_splits = plan.sk_splits;
+  params.dyn_pieces = plan.dyn_pieces;
+  params.dyn_ppt = plan.dyn_ppt;
+  params.dyn_piece_kb = plan.dyn_piece_kb;
+  params.dyn_static_kb = plan.dyn_static_kb;
   params.max_contrib = plan.max_contrib;
   params.status = st->status_dev;
   if (fusion.on) {
@@ -593,8 +616,10 @@ int gemm_device(const void* A, const void* B, void* C, int64_t M, int64_t N, int
     }
     params.tile_counters = reinterpret_cast<int*>(ws);
     params.partials = reinterpret_cast<float*>(ws + plan.counters_bytes);
-    params.counters_len = static_cast<long long>(plan.counters_bytes / sizeof(int));
+    // The last word of the counter region is the claim counter of the dynamic tail pool.
+    params.counters_len = static_cast<long long>(plan.counters_bytes / sizeof(int)) - 1;
     params.partials_elems = static_cast<long long>(plan.partials_bytes / sizeof(float));
+    params.dyn_counter = reinterpret_cast<int*>(ws) + params.counters_len;
   }
 
   t_last_config[0] = plan.cta_group;
@@ -790,7 +815,8 @@ int neogemm_set_phase_timers(void* device_buffer, size_t bytes) {
 }
 
 int neogemm_set_tuning(int key, int value) {
-  if (key < 0 || key > 3 || value > 1000000 || (key == 0 && value > 7) || (key == 3 && value > 1))
+  if (key < 0 || key > 4 || value > 1000000 || (key == 0 && value > 7) || (key == 3 && value > 1) ||
+      (key == 4 && value > 4))
     return NEOGEMM_ERR_BAD_ARG;
   t_override.tuning[key] = value;
   return NEOGEMM_OK;
@@ -822,6 +848,10 @@ int neogemm_debug_plan(int64_t M, int64_t N, int64_t K, int64_t ldc, int c_col_m
   params.stream_k = plan.stream_k ? 1 : 0;
   params.sk_first_tile = plan.sk_first_tile;
   params.sk_splits = plan.sk_splits;
+  params.dyn_pieces = plan.dyn_pieces;
+  params.dyn_ppt = plan.dyn_ppt;
+  params.dyn_piece_kb = plan.dyn_piece_kb;
+  params.dyn_static_kb = plan.dyn_static_kb;
   const int workers = plan.num_ctas / plan.cta_group;
   int count = 0;
   for (int w = 0; w < workers; ++w) {
@@ -833,6 +863,23 @@ int neogemm_debug_plan(int64_t M, int64_t N, int64_t K, int64_t ldc, int c_col_m
         tile_coords(params, seg.tile, tm, tn);
         int* o = segments + 8 * count;
         o[0] = w; o[1] = seg.tile; o[2] = seg.kb_begin; o[3] = seg.kb_count;
+        o[4] = seg.contrib; o[5] = seg.n_contrib; o[6] = tm; o[7] = tn;
+      }
+      ++count;
+    }
+  }
+  // Pieces of the dynamic tail pool: who computes them is decided at run time; they are listed
+  // with the worker that would take them if claims came round-robin.
+  if (plan.dyn_pieces > 0) {
+    SegmentIter it(params, 0, workers);
+    for (int id = 0; id < plan.dyn_pieces; ++id) {
+      Segment seg;
+      it.piece(seg, id);
+      if (segments != nullptr && count < max_segments) {
+        int tm, tn;
+        tile_coords(params, seg.tile, tm, tn);
+        int* o = segments + 8 * count;
+        o[0] = id % workers; o[1] = seg.tile; o[2] = seg.kb_begin; o[3] = seg.kb_count;
         o[4] = seg.contrib; o[5] = seg.n_contrib; o[6] = tm; o[7] = tn;
       }
       ++count;
@@ -1018,6 +1065,10 @@ int neogemm_bf16_nt_noalloc(const void* A, const void* B, void* C, int64_t M, in
   params.stream_k = plan.stream_k ? 1 : 0;
   params.sk_first_tile = plan.sk_first_tile;
   params.sk_splits = plan.sk_splits;
+  params.dyn_pieces = plan.dyn_pieces;
+  params.dyn_ppt = plan.dyn_ppt;
+  params.dyn_piece_kb = plan.dyn_piece_kb;
+  params.dyn_static_kb = plan.dyn_static_kb;
   params.max_contrib = plan.max_contrib;
   params.status = st->status;
   params.timers = nullptr;
@@ -1030,8 +1081,9 @@ int neogemm_bf16_nt_noalloc(const void* A, const void* B, void* C, int64_t M, in
     }
     params.tile_counters = reinterpret_cast<int*>(st->scratch);
     params.partials = reinterpret_cast<float*>(st->scratch + plan.counters_bytes);
-    params.counters_len = static_cast<long long>(plan.counters_bytes / sizeof(int));
+    params.counters_len = static_cast<long long>(plan.counters_bytes / sizeof(int)) - 1;
     params.partials_elems = static_cast<long long>(plan.partials_bytes / sizeof(float));
+    params.dyn_counter = reinterpret_cast<int*>(st->scratch) + params.counters_len;
   }
   return launch(&st->launch_state, plan, mx, my, md, params, stream);
 }

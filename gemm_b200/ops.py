@@ -198,7 +198,8 @@ def set_override(cta_group: int = -1, block_n: int = -1, swap: int = -1, stream_
     check(lib.neogemm_set_override(cta_group, block_n, swap, stream_k, group_m, max_ctas))
 
 
-TUNING_KEYS = {"l2_hints": 0, "epilogue_wait_hint_ns": 1, "ring_wait_hint_ns": 2, "wide_tile": 3}
+TUNING_KEYS = {"l2_hints": 0, "epilogue_wait_hint_ns": 1, "ring_wait_hint_ns": 2, "wide_tile": 3,
+               "dynamic_pieces_per_tile": 4}
 
 
 def set_tuning(key: str, value: int = -1) -> None:

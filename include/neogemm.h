@@ -126,7 +126,8 @@ int neogemm_bf16_nt_host(const void* A_host, const void* B_host, void* C_host,
 
 /* Device-side error record of the current device: out[0] = code (0 none; 1 producer wait expired,
  * 2 MMA operand wait, 3 MMA accumulator wait, 4 epilogue wait, 5 tensor-memory address,
- * 6 an index failed the kernel's own bounds check and the access was skipped),
+ * 6 an index failed the kernel's own bounds check and the access was skipped, 7 a wait on the
+ * run-time work queue expired),
  * out[1] = CTA index, out[2] = segment index, out[3] = ring stage or accumulator.  Meaningful once
  * the stream of the launch has been synchronised.  The reference only prints cudaGetLastError
  * (nemgemmV03.cu:387-390). */
@@ -160,6 +161,8 @@ int neogemm_set_override(int cta_group, int block_n, int swap, int stream_k, int
  *   key 2: the same for the TMA producer's and the MMA warp's waits on the operand ring.
  *   key 3: the 256 x 512 pair tile (two UMMA-N halves sharing one operand): 0 never, 1 whenever
  *          the shape allows, -1 chosen by estimated time.
+ *   key 4: pieces (of 16 k-blocks) per tile that the stream-K schedule of skinny shapes leaves to
+ *          be claimed at run time instead of assigning them statically (0 = none, up to 4).
  * No counterpart in the reference (its maps only set L2 promotion, nemgemmV03.cu:52). */
 int neogemm_set_tuning(int key, int value);
 

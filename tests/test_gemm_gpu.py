@@ -222,3 +222,33 @@ def test_torch_extension_module_matches_reference_usage():
 def test_device_status_is_clean_after_all_of_the_above():
     torch.cuda.synchronize()
     assert ops.device_status() == (0, 0, 0, 0)
+
+
+@pytest.mark.parametrize("case", [
+    ((16, 3584, 8192), None, None),            # default: one run-time piece per tile
+    ((64, 3584, 4096), 2, None),
+    ((128, 2048, 8192), 4, None),
+    ((24, 1000, 4096), 3, 5),                  # ragged tiles, few CTAs, many claims each
+    ((32, 28672, 8192), 1, None),
+])
+def test_dynamic_tail_pool(case):
+    # The last k-blocks of every tile are claimed at run time; who computes them varies from
+    # launch to launch, the bits must not.
+    (M, N, K), pieces, ctas = case
+    tuning = {} if pieces is None else {"dynamic_pieces_per_tile": pieces}
+    ov = dict(stream_k=1, swap=1, max_ctas=ctas) if ctas else None
+    stats, cfg = run_case(M, N, K, tuning=tuning, override=ov)
+    assert cfg["stream_k"] == 1 and cfg["swap"] == 1, cfg
+    A, B = make_problem(M, N, K, seed=99)
+    dA, dB = A.cuda(), B.cuda()
+    for key, value in tuning.items():
+        ops.set_tuning(key, value)
+    try:
+        first = ops.matmul(dA, dB).clone()
+        for _ in range(8):
+            assert torch.equal(first.view(torch.int16), ops.matmul(dA, dB).view(torch.int16))
+    finally:
+        for key in tuning:
+            ops.set_tuning(key, -1)
+    torch.cuda.synchronize()
+    assert ops.device_status()[0] == 0

@@ -15,17 +15,21 @@ PLAN_KEYS = ("cta_group", "block_n", "stages", "swap", "stream_k", "ctas", "tile
              "epi", "Md", "Nd", "m_tiles", "n_tiles", "k_blocks", "max_contrib", "sk_first")
 
 
-def plan(M, N, K, ldc=None, col_major=False, sm=148, override=None, max_seg=400000):
+def plan(M, N, K, ldc=None, col_major=False, sm=148, override=None, max_seg=400000, tuning=None):
     ldc = (M if col_major else N) if ldc is None else ldc
     po = (ctypes.c_int * 16)()
     seg = (ctypes.c_int * (8 * max_seg))()
     if override:
         assert lib.neogemm_set_override(*override) == 0
+    for key, value in (tuning or {}).items():
+        assert lib.neogemm_set_tuning(key, value) == 0
     try:
         n = lib.neogemm_debug_plan(ctypes.c_int64(M), ctypes.c_int64(N), ctypes.c_int64(K),
                                    ctypes.c_int64(ldc), 1 if col_major else 0, sm, po, seg, max_seg)
     finally:
         lib.neogemm_set_override(-1, -1, -1, -1, -1, -1)
+        for key in (tuning or {}):
+            lib.neogemm_set_tuning(key, -1)
     assert n >= 0, f"plan failed with status {-n}"
     assert n <= max_seg
     segs = [tuple(seg[8 * i:8 * i + 8]) for i in range(n)]
@@ -75,12 +79,27 @@ def test_decode_shapes_use_swapped_stream_k(M):
     assert (p["swap"], p["stream_k"], p["cta_group"]) == (1, 1, 1)
     assert p["block_n"] == M and p["Md"] == 28672 and p["tiles"] == 224 and p["ctas"] == 148
     check_cover(p, segs)
-    # equal byte streams: every CTA gets 193 or 194 of the 28672 (tile, k-block) units
+    # For M <= 32 the last 16 k-blocks of every tile are the dynamic tail pool: fixed pieces
+    # claimed at run time.  The rest is cut into equal static ranges.
+    ppt = 1 if M <= 32 else 0
+    static_kb = 128 - 16 * ppt
+    pieces = [s for s in segs if s[2] >= static_kb]
+    static = [s for s in segs if s[2] < static_kb]
+    assert len(pieces) == 224 * ppt and all(s[3] == 16 for s in pieces)
+    assert all(s[2] + s[3] <= static_kb for s in static)
+    per_worker = defaultdict(int)
+    for s in static:
+        per_worker[s[0]] += s[3]
+    lo = 224 * static_kb // 148
+    assert set(per_worker.values()) <= {lo, lo + 1} and len(per_worker) == 148
+    assert p["max_contrib"] == 2 + ppt
+    # switched off, every CTA gets 193 or 194 of the 28672 (tile, k-block) units
+    p, segs = plan(M, 28672, 8192, tuning={4: 0})
+    check_cover(p, segs)
     per_worker = defaultdict(int)
     for s in segs:
         per_worker[s[0]] += s[3]
-    assert set(per_worker.values()) <= {193, 194} and len(per_worker) == 148
-    assert p["max_contrib"] == 2
+    assert set(per_worker.values()) <= {193, 194} and p["max_contrib"] == 2
 
 
 @pytest.mark.parametrize("sm", [1, 2, 3, 7, 16, 132, 148, 160])
