@@ -53,7 +53,8 @@ struct GemmParams {
   int num_m_tiles, num_n_tiles, num_tiles, num_k_blocks;
   int group_m;               // tile rows per raster group (L2 reuse)
   int l2_hints;              // bit 0: X loads evict-last, bit 1: Y loads evict-first,
-                             // bit 2: D stores evict-first (0 = no hints)
+                             // bit 2: D stores evict-first, bit 3: X loads evict-first,
+                             // bit 4: Y loads evict-last (0 = no hints)
   int epi_wait_hint_ns;      // suspend hint of the epilogue's wait for an accumulator (0 = none)
   int main_wait_hint_ns;     // suspend hint of the producer's and the MMA warp's ring waits
   // Direct epilogue / split partials.
@@ -444,13 +445,12 @@ __device__ __forceinline__ void fused_epilogue(uint32_t (&r)[kN], const GemmPara
 // from r[] itself, so the result does not depend on which contributor arrived last.  `col_base`
 // points at this row's entry of the first of the kN columns in contributor 0's slot; consecutive
 // columns are `col_stride` floats apart and consecutive contributors `slot_stride`.
-template <int kN>
+template <int kN, int kGroup = ((kN <= 16) ? 4 : 1)>
 __device__ __forceinline__ void sum_partials(uint32_t (&r)[kN], const float* col_base,
                                              size_t col_stride, size_t slot_stride, int contrib,
                                              int n_contrib) {
   // Up to kGroup contributors' loads are issued before any is consumed (kGroup * kN independent
   // loads in flight per thread, each a 128-byte line per warp), then added in contributor order.
-  constexpr int kGroup = (kN <= 16) ? 4 : 2;
   float sum[kN];
 #pragma unroll 1
   for (int q0 = 0; q0 < n_contrib; q0 += kGroup) {
@@ -567,8 +567,9 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
       const uint32_t leader_full = (kCtaGroup == 2) ? mapa_u32(full_bar, 0) : full_bar;
       // X is the operand the raster keeps across consecutive waves (a group of tile rows); Y
       // streams past it.
-      const bool hint_x = (p.l2_hints & 1) != 0, hint_y = (p.l2_hints & 2) != 0;
-      const uint64_t pol_x = l2_policy_evict_last(), pol_y = l2_policy_evict_first();
+      const bool hint_x = (p.l2_hints & 9) != 0, hint_y = (p.l2_hints & 18) != 0;
+      const uint64_t pol_x = (p.l2_hints & 8) ? l2_policy_evict_first() : l2_policy_evict_last();
+      const uint64_t pol_y = (p.l2_hints & 16) ? l2_policy_evict_last() : l2_policy_evict_first();
       bool ok = true;
       GemmParams timer_params = p;
       if (lane != 0) timer_params.timers = nullptr;
@@ -910,9 +911,17 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
             const float* base = tile_partials + static_cast<size_t>(c) * Cfg::TILE_M +
                                 cta_rank * Cfg::BLOCK_M + row_in_cta;
             const size_t slot = static_cast<size_t>(BLOCK_N) * Cfg::TILE_M;
-            sum_partials<32>(r0, base, Cfg::TILE_M, slot, seg.contrib, seg.n_contrib);
-            sum_partials<32>(r1, base + 32 * Cfg::TILE_M, Cfg::TILE_M, slot, seg.contrib,
-                             seg.n_contrib);
+            // 16 columns at a time, one contributor in flight: this path is rare (cut last wave)
+            // and must not cost the plain path registers.
+            using Quarter = uint32_t(&)[16];
+            sum_partials<16, 1>(reinterpret_cast<Quarter>(r0[0]), base, Cfg::TILE_M, slot,
+                                seg.contrib, seg.n_contrib);
+            sum_partials<16, 1>(reinterpret_cast<Quarter>(r0[16]), base + 16 * Cfg::TILE_M,
+                                Cfg::TILE_M, slot, seg.contrib, seg.n_contrib);
+            sum_partials<16, 1>(reinterpret_cast<Quarter>(r1[0]), base + 32 * Cfg::TILE_M,
+                                Cfg::TILE_M, slot, seg.contrib, seg.n_contrib);
+            sum_partials<16, 1>(reinterpret_cast<Quarter>(r1[16]), base + 48 * Cfg::TILE_M,
+                                Cfg::TILE_M, slot, seg.contrib, seg.n_contrib);
           }
           if (p.fuse) {
             fused_epilogue<32>(r0, p, row0 + row_in_cta, col0 + c);
@@ -957,50 +966,52 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
                      ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
         const uint32_t stg = epi_base + (warp - 2) * Cfg::SMEM_EPI_T_WARP;
         if (transposed) __syncwarp();   // the previous tile's write-out has left the staging
+        // 32 columns per step where the tile has them: half as many dependent round trips to
+        // the partials of a cut tile as with 16.
+        constexpr int kDC = (BLOCK_N >= 32) ? 32 : 16;
 #pragma unroll 1
-        for (int c = 0; c < BLOCK_N; c += 16) {
-          uint32_t r[16];
+        for (int c = 0; c < BLOCK_N; c += kDC) {
+          uint32_t r[kDC];
           // tcgen05.ld / wait::ld are .sync.aligned: every lane must arrive together.  Lanes
           // whose row is out of range skip the stores below and would otherwise run ahead.
           __syncwarp();
-          tmem_ld_32x32b_x16(taddr + c, r);
+          if constexpr (kDC == 32) tmem_ld_32x32b_x32(taddr + c, r);
+          else tmem_ld_32x32b_x16(taddr + c, r);
           tmem_ld_wait();
           if (tile_partials != nullptr) {
-            sum_partials<16>(r, tile_partials + static_cast<size_t>(c) * Cfg::TILE_M +
-                                    cta_rank * Cfg::BLOCK_M + row_in_cta,
-                             Cfg::TILE_M, static_cast<size_t>(BLOCK_N) * Cfg::TILE_M, seg.contrib,
-                             seg.n_contrib);
+            sum_partials<kDC>(r, tile_partials + static_cast<size_t>(c) * Cfg::TILE_M +
+                                     cta_rank * Cfg::BLOCK_M + row_in_cta,
+                              Cfg::TILE_M, static_cast<size_t>(BLOCK_N) * Cfg::TILE_M, seg.contrib,
+                              seg.n_contrib);
           }
           const int col = col0 + c;
-          if (p.fuse) fused_epilogue<16>(r, p, row, col);
+          if (p.fuse) fused_epilogue<kDC>(r, p, row, col);
           if (transposed) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
+            for (int j = 0; j < kDC; ++j)
               st_shared_b16(stg + static_cast<uint32_t>(c + j) * 64u + lane * 2u,
                             __bfloat16_as_ushort(__float2bfloat16_rn(__uint_as_float(r[j]))));
           } else
           if (row < p.Md && col < p.Nd) {
-            const int last_col = min(col + 15, p.Nd - 1);
+            const int last_col = min(col + kDC - 1, p.Nd - 1);
             const long long last = static_cast<long long>(row) * p.out_stride_r +
                                    static_cast<long long>(last_col) * p.out_stride_c;
             if (last >= p.out_span) {
               report_error(p, abort_flag, kDevBounds, seg_idx, 3);
             } else
-            if (vec_ok && col + 16 <= p.Nd) {
-              uint4 v0, v1;
-              v0.x = pack_bf16x2(__uint_as_float(r[0]), __uint_as_float(r[1]));
-              v0.y = pack_bf16x2(__uint_as_float(r[2]), __uint_as_float(r[3]));
-              v0.z = pack_bf16x2(__uint_as_float(r[4]), __uint_as_float(r[5]));
-              v0.w = pack_bf16x2(__uint_as_float(r[6]), __uint_as_float(r[7]));
-              v1.x = pack_bf16x2(__uint_as_float(r[8]), __uint_as_float(r[9]));
-              v1.y = pack_bf16x2(__uint_as_float(r[10]), __uint_as_float(r[11]));
-              v1.z = pack_bf16x2(__uint_as_float(r[12]), __uint_as_float(r[13]));
-              v1.w = pack_bf16x2(__uint_as_float(r[14]), __uint_as_float(r[15]));
-              *reinterpret_cast<uint4*>(out_row + col) = v0;
-              *reinterpret_cast<uint4*>(out_row + col + 8) = v1;
+            if (vec_ok && col + kDC <= p.Nd) {
+#pragma unroll
+              for (int v8 = 0; v8 < kDC / 8; ++v8) {
+                uint4 v;
+                v.x = pack_bf16x2(__uint_as_float(r[8 * v8 + 0]), __uint_as_float(r[8 * v8 + 1]));
+                v.y = pack_bf16x2(__uint_as_float(r[8 * v8 + 2]), __uint_as_float(r[8 * v8 + 3]));
+                v.z = pack_bf16x2(__uint_as_float(r[8 * v8 + 4]), __uint_as_float(r[8 * v8 + 5]));
+                v.w = pack_bf16x2(__uint_as_float(r[8 * v8 + 6]), __uint_as_float(r[8 * v8 + 7]));
+                *reinterpret_cast<uint4*>(out_row + col + 8 * v8) = v;
+              }
             } else {
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
+              for (int j = 0; j < kDC; ++j) {
                 if (col + j < p.Nd)
                   out_row[static_cast<long long>(col + j) * p.out_stride_c] =
                       __float2bfloat16_rn(__uint_as_float(r[j]));

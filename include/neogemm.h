@@ -155,12 +155,13 @@ int neogemm_set_override(int cta_group, int block_n, int swap, int stream_k, int
 /* Tuning knobs of the calling thread; value -1 restores the library default.
  *   key 0: L2 eviction hints of the TMA copies.  Bit 0: loads of the operand on the 128-lane axis
  *          are evict-last; bit 1: loads of the other operand are evict-first; bit 2: stores of C
- *          are evict-first.
+ *          are evict-first; bit 3: 128-lane operand evict-first; bit 4: other operand evict-last.
  *   key 1: nanoseconds the epilogue warps may stay suspended in one mbarrier.try_wait while they
  *          wait for a finished accumulator (0 = plain try_wait).
  *   key 2: the same for the TMA producer's and the MMA warp's waits on the operand ring.
  *   key 3: the 256 x 512 pair tile (two UMMA-N halves sharing one operand): 0 never, 1 whenever
  *          the shape allows, -1 chosen by estimated time.
+ *   key 5: L2 promotion of the TMA loads: 0 none, 1 64 B, 2 128 B, 3 256 B (default).
  *   key 4: pieces (of 16 k-blocks) per tile that the stream-K schedule of skinny shapes leaves to
  *          be claimed at run time instead of assigning them statically (0 = none, up to 4).
  * No counterpart in the reference (its maps only set L2 promotion, nemgemmV03.cu:52). */
