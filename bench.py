@@ -48,9 +48,9 @@ WORKLOADS = {
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch of the dominant kernel,
 # from the ncu captures summarised under profiles/ (same bench.py command lines).
 NCU_TRAFFIC_BYTES = {
-    "8192": 1068594000 + 127370240,
-    "decode16": 472501760 + 5468416,
-    "decode128": 482692608 + 20661760,
+    "8192": 912804608 + 120428800,
+    "decode16": 471264512 + 4690944,
+    "decode128": 473134848 + 11559424,
 }
 
 
