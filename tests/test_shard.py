@@ -119,3 +119,23 @@ def test_overlapped_broadcast_on_two_gloo_ranks(tmp_path):
     mp.spawn(_worker_overlap, args=(world, _free_port(), 200, 700, 64, str(tmp_path)),
              nprocs=world, join=True)
     assert all((tmp_path / f"ok{r}").exists() for r in range(world))
+
+
+@pytest.mark.gpu
+@pytest.mark.timeout(600)
+def test_sharded_product_on_the_gpus_of_this_box():
+    """One process per GPU over NCCL (needs at least two GPUs; skipped on a single-GPU box)."""
+    import subprocess
+    import sys
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    world = 2 if n < 4 else 4
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
+           os.path.join(root, "tests", "run_sharded_gpu.py")]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=540, env=env)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
+    assert out.stdout.count("sharded parity ok") == world
