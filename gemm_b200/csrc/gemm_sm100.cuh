@@ -873,7 +873,62 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
       if (!finish) {
         // nothing to store: another contributor completes these rows
       } else
-      if (Cfg::kEpiMode == kEpiTmaStore) {
+      if constexpr (Cfg::kEpiMode == kEpiTmaStore && Cfg::kNHalves == 2) {
+        // Two-half tile: all 512 TMEM columns belong to this tile, so the next tile's MMAs wait
+        // for this read-out.  Keep it free of anything slow: this warp's share (32 rows x 128
+        // columns of each half) is pulled into registers as packed bf16 - half 0, hand it back,
+        // half 1, hand it back - and only then goes through the staging buffer and the TMA
+        // stores, whose shared-memory read-out takes about a microsecond per box.
+        const uint32_t buf = epi_base + (warp - 2) * Cfg::SMEM_EPI_WARP_BUF;
+        const int my_row0 = row0 + quad * 32;
+        uint32_t packed[2][64];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+          for (int part = 0; part < 4; ++part) {
+            const int c = h * BLOCK_N + warp_set * (BLOCK_N / 2) + part * 32;
+            uint32_t r[32];
+            __syncwarp();
+            tmem_ld_32x32b_x32(taddr + c, r);
+            tmem_ld_wait();
+            if (p.fuse) fused_epilogue<32>(r, p, row0 + row_in_cta, col0 + c);
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              packed[h][part * 16 + j] =
+                  pack_bf16x2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+          }
+          tcgen05_fence_before();
+          __syncwarp();
+          if (lane == 0) {
+            if (kCtaGroup == 2) mbar_arrive_cluster(leader_tmem_empty + 8 * h);
+            else mbar_arrive(tmem_empty_bar + 8 * h);
+          }
+        }
+        released = true;
+        const uint32_t row_addr = buf + lane * 128u;
+        const uint32_t sw = lane & 7u;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int h = i >> 1, b = i & 1;
+          const int c = h * BLOCK_N + warp_set * (BLOCK_N / 2) + b * Cfg::EPI_COLS;
+          if (lane == 0) tma_store_wait_read<0>();   // the previous box has left the buffer
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            st_shared_v4(row_addr + ((static_cast<uint32_t>(j) ^ sw) << 4),
+                         packed[h][b * 32 + 4 * j + 0], packed[h][b * 32 + 4 * j + 1],
+                         packed[h][b * 32 + 4 * j + 2], packed[h][b * 32 + 4 * j + 3]);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (my_row0 < p.Md && col0 + c < p.Nd) {
+              if (p.l2_hints & 4) tma_store_2d_hint(&tmap_d, buf, col0 + c, my_row0, pol_d);
+              else tma_store_2d(&tmap_d, buf, col0 + c, my_row0);
+            }
+            tma_store_commit();
+          }
+        }
+      } else if (Cfg::kEpiMode == kEpiTmaStore) {
         const uint32_t warp_stage = epi_base + (warp - 2) * Cfg::kEpiBufs * Cfg::SMEM_EPI_WARP_BUF;
         const int my_row0 = row0 + quad * 32;
         // One-half tiles: this warp walks all BLOCK_N columns.  Two-half tiles: the two sets of
