@@ -37,6 +37,8 @@ constexpr int kDefaultTuning[3] = {0, 2000, 0};
 constexpr double kWideTileSpeed = 1650.0;
 // k-blocks per dynamically claimed piece of the stream-K tail pool.
 constexpr int kDynPieceKBlocks = 16;
+// Row chunks the host entry point cuts the uploaded operand into (one product launch each).
+constexpr int kMaxHostChunks = 16;
 // Pieces per tile left to the pool unless tuning key 4 says otherwise.
 constexpr int kDefaultDynPieces = 1;
 
@@ -103,6 +105,9 @@ struct DeviceState {
   void* stage[3] = {nullptr, nullptr, nullptr};  // device copies of A, B, C for the host entry
   size_t stage_bytes[3] = {0, 0, 0};
   bool attr_done[16] = {};
+  // Host entry point: copy queues for the two PCIe directions and the events that order them.
+  cudaStream_t copy_in = nullptr, copy_out = nullptr;
+  cudaEvent_t copy_events[2 * 16 + 1] = {};
 };
 
 DeviceState g_dev[kMaxDevices];
@@ -190,7 +195,7 @@ struct MapSlot {
   CUtensorMap map;
 };
 thread_local std::vector<MapSlot> t_map_cache;  // most recently used at the back
-constexpr size_t kMapCacheSize = 32;
+constexpr size_t kMapCacheSize = 128;
 
 // Row-major bf16 matrix [rows, inner] with row pitch `pitch_bytes`; box = 64 elements (one
 // 128-byte swizzle row) x box_rows; out-of-range elements read as zero and are not written.
@@ -652,6 +657,23 @@ int gemm_device(const void* A, const void* B, void* C, int64_t M, int64_t N, int
   return launch(st, plan, mx, my, md, params, stream);
 }
 
+int ensure_copy_queues(DeviceState* st) {
+  if (st->copy_in != nullptr) return NEOGEMM_OK;
+  if (cudaStreamCreateWithFlags(&st->copy_in, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaStreamCreateWithFlags(&st->copy_out, cudaStreamNonBlocking) != cudaSuccess) {
+    cudaGetLastError();
+    st->copy_in = nullptr;
+    return NEOGEMM_ERR_CUDA;
+  }
+  for (cudaEvent_t& e : st->copy_events) {
+    if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) {
+      cudaGetLastError();
+      return NEOGEMM_ERR_CUDA;
+    }
+  }
+  return NEOGEMM_OK;
+}
+
 int ensure_stage(DeviceState* st, int which, size_t bytes) {
   if (bytes <= st->stage_bytes[which]) return NEOGEMM_OK;
   if (st->stage[which] != nullptr) cudaFree(st->stage[which]);
@@ -736,21 +758,69 @@ int neogemm_bf16_nt_host(const void* A_host, const void* B_host, void* C_host, i
     if ((rc = ensure_stage(st, 0, std::max<size_t>(bytes_a, 16))) != NEOGEMM_OK) return rc;
     if ((rc = ensure_stage(st, 1, std::max<size_t>(bytes_b, 16))) != NEOGEMM_OK) return rc;
     if ((rc = ensure_stage(st, 2, bytes_c)) != NEOGEMM_OK) return rc;
+    if ((rc = ensure_copy_queues(st)) != NEOGEMM_OK) return rc;
   }
+  // The rows of the matrix as stored ([M,N], or [N,M] for column-major C) come from one operand
+  // (U); the other (V) is needed whole.  V goes up first; then U goes up in row chunks, each
+  // chunk's product is launched as soon as it has landed, and its rows of C go back down while
+  // the next chunk is still going up: the two PCIe directions and the GPU work overlap, so the
+  // call takes about as long as the uploads alone.
+  const int64_t pm = c_col_major ? N : M;
+  const int64_t pn = c_col_major ? M : N;
+  const char* U_host = static_cast<const char*>(c_col_major ? B_host : A_host);
+  const char* V_host = static_cast<const char*>(c_col_major ? A_host : B_host);
+  char* dU = static_cast<char*>(c_col_major ? st->stage[1] : st->stage[0]);
+  char* dV = static_cast<char*>(c_col_major ? st->stage[0] : st->stage[1]);
+  char* dC = static_cast<char*>(st->stage[2]);
+  const size_t bytes_v = c_col_major ? bytes_a : bytes_b;
+  int64_t chunks = std::min<int64_t>(kMaxHostChunks, std::max<int64_t>(1, pm / 1024));
+  if (K == 0) chunks = 1;
+  const int64_t chunk_rows = ((pm + chunks - 1) / chunks + 255) / 256 * 256;
+
+  auto fail = [&](int code) {
+    cudaGetLastError();
+    cudaStreamSynchronize(st->copy_in);
+    cudaStreamSynchronize(st->copy_out);
+    cudaStreamSynchronize(stream);
+    cudaGetLastError();
+    return code;
+  };
+  cudaEvent_t* ev = st->copy_events;
+  // Everything below starts after the work already queued on the caller's stream.
+  if (cudaEventRecord(ev[0], stream) != cudaSuccess ||
+      cudaStreamWaitEvent(st->copy_in, ev[0], 0) != cudaSuccess ||
+      cudaStreamWaitEvent(st->copy_out, ev[0], 0) != cudaSuccess)
+    return fail(NEOGEMM_ERR_CUDA);
   if (K > 0) {
-    if (cudaMemcpyAsync(st->stage[0], A_host, bytes_a, cudaMemcpyHostToDevice, stream) !=
-            cudaSuccess ||
-        cudaMemcpyAsync(st->stage[1], B_host, bytes_b, cudaMemcpyHostToDevice, stream) !=
-            cudaSuccess) {
-      cudaGetLastError();
-      return NEOGEMM_ERR_CUDA;
-    }
+    if (cudaMemcpyAsync(dV, V_host, bytes_v, cudaMemcpyHostToDevice, st->copy_in) != cudaSuccess)
+      return fail(NEOGEMM_ERR_CUDA);
   }
-  rc = gemm_device(st->stage[0], st->stage[1], st->stage[2], M, N, K, K, K, c_col_major ? M : N,
-                   c_col_major, nullptr, 0, stream);
-  if (rc != NEOGEMM_OK) return rc;
-  if (cudaMemcpyAsync(C_host, st->stage[2], bytes_c, cudaMemcpyDeviceToHost, stream) !=
-          cudaSuccess ||
+  int64_t index = 0;
+  for (int64_t r0 = 0; r0 < pm; r0 += chunk_rows, ++index) {
+    const int64_t rows = std::min(chunk_rows, pm - r0);
+    cudaEvent_t up = ev[1 + 2 * index], done = ev[2 + 2 * index];
+    if (K > 0 &&
+        cudaMemcpyAsync(dU + r0 * K * 2, U_host + r0 * K * 2, static_cast<size_t>(rows) * K * 2,
+                        cudaMemcpyHostToDevice, st->copy_in) != cudaSuccess)
+      return fail(NEOGEMM_ERR_CUDA);
+    if (cudaEventRecord(up, st->copy_in) != cudaSuccess ||
+        cudaStreamWaitEvent(stream, up, 0) != cudaSuccess)
+      return fail(NEOGEMM_ERR_CUDA);
+    if (c_col_major)
+      rc = gemm_device(dV, dU + r0 * K * 2, dC + r0 * pn * 2, M, rows, K, K, K, M, 1, nullptr, 0,
+                       stream);
+    else
+      rc = gemm_device(dU + r0 * K * 2, dV, dC + r0 * pn * 2, rows, N, K, K, K, N, 0, nullptr, 0,
+                       stream);
+    if (rc != NEOGEMM_OK) return fail(rc);
+    if (cudaEventRecord(done, stream) != cudaSuccess ||
+        cudaStreamWaitEvent(st->copy_out, done, 0) != cudaSuccess ||
+        cudaMemcpyAsync(static_cast<char*>(C_host) + r0 * pn * 2, dC + r0 * pn * 2,
+                        static_cast<size_t>(rows) * pn * 2, cudaMemcpyDeviceToHost,
+                        st->copy_out) != cudaSuccess)
+      return fail(NEOGEMM_ERR_CUDA);
+  }
+  if (cudaStreamSynchronize(st->copy_out) != cudaSuccess ||
       cudaStreamSynchronize(stream) != cudaSuccess) {
     cudaGetLastError();
     return NEOGEMM_ERR_CUDA;

@@ -115,7 +115,11 @@ int neogemm_bf16_nt_noalloc(const void* A, const void* B, void* C,
 size_t neogemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int c_col_major);
 
 /* Same product with HOST buffers: copies A and B to the device, runs the kernel and copies C
- * back, all on `stream`, then synchronises the stream.  Packed layouts (lda = ldb = K; ldc = N, or
+ * back, then waits.  The work is ordered after what is already queued on `stream`; internally
+ * the operand that indexes the stored rows of C goes up in row chunks on a copy queue of the
+ * library's own, each chunk's product is launched on `stream` as it lands and its rows of C
+ * return on a second copy queue, so that both PCIe directions and the GPU overlap (pinned host
+ * memory is needed for that; pageable memory works but serialises).  Packed layouts (lda = ldb = K; ldc = N, or
  * M when c_col_major).  Device staging buffers are owned by the library and reused across calls.
  * This is the call a host program without device memory of its own makes; the reference's
  * counterpart is the cublass/matmul.cu flow (host malloc -> cudaMemcpy -> kernel -> cudaMemcpy,

@@ -166,6 +166,21 @@ def test_host_entry_point_round_trip():
     oracle.assert_parity(Cc.t(), oracle.gemm_fp32(A, B), "host entry column-major")
 
 
+def test_host_entry_point_pipelines_large_operands():
+    # More than 1024 stored rows: the upload goes in row chunks, one product launch per chunk,
+    # results return while the next chunk is still going up.  Ragged last chunk on purpose.
+    M, N, K = 4000, 1032, 520
+    A, B = make_problem(M, N, K, seed=23)
+    ref = oracle.gemm_fp32(A, B)
+    C = torch.full((M, N), float("nan"), dtype=torch.bfloat16).pin_memory()
+    ops.matmul_host(A.pin_memory(), B.pin_memory(), C)
+    oracle.assert_parity(C, ref, "host entry, chunked rows of A")
+    Cc = torch.full((N, M), float("nan"), dtype=torch.bfloat16).pin_memory()
+    ops.matmul_host(A.pin_memory(), B.pin_memory(), Cc, col_major=True)   # chunks run over B
+    oracle.assert_parity(Cc.t(), ref, "host entry column-major, chunked rows of B")
+    assert ops.device_status()[0] == 0
+
+
 def test_runs_on_a_side_stream():
     A, B = make_problem(512, 768, 512, seed=31)
     dA, dB = A.cuda(), B.cuda()
