@@ -1143,4 +1143,28 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
   if (threadIdx.x == 0) PhaseTimer(p).stamp(12);
 }
 
+// Self-test of the bounded-wait machinery: one warp waits, with the given limit, on an mbarrier
+// that nothing will ever arrive on, and must come back with the limit expired, record the error
+// like the GEMM roles do and exit normally.  No fault, no trap: the wait simply runs out.
+__global__ void wait_expiry_selftest_kernel(GemmParams p, unsigned long long limit_ns,
+                                            unsigned long long* waited_ns) {
+  __shared__ __align__(8) unsigned long long bar;
+  __shared__ int abort_word;
+  const uint32_t bar_addr = ptx::smem_u32(&bar);
+  if (threadIdx.x == 0) {
+    abort_word = 0;
+    ptx::mbar_init(bar_addr, 1);
+    ptx::fence_barrier_init();
+  }
+  __syncthreads();
+  const uint64_t t0 = ptx::globaltimer_ns();
+  const bool completed = __all_sync(
+      0xffffffffu, ptx::mbar_wait(bar_addr, 0, &abort_word, 0, limit_ns));
+  const uint64_t t1 = ptx::globaltimer_ns();
+  if (!completed && threadIdx.x == 0) {
+    report_error(p, &abort_word, kDevTimeoutEpilogue, /*segment*/ -1, /*aux*/ -1);
+    if (waited_ns != nullptr) *waited_ns = t1 - t0;
+  }
+}
+
 }  // namespace neogemm

@@ -909,6 +909,34 @@ int neogemm_set_tuning(int key, int value) {
   return NEOGEMM_OK;
 }
 
+int neogemm_debug_wait_expiry(unsigned int limit_us, unsigned long long* waited_ns_out) {
+  if (limit_us == 0 || limit_us > 100000) return NEOGEMM_ERR_BAD_ARG;   // 0.1 s at most
+  int rc;
+  DeviceState* st;
+  {
+    std::lock_guard<std::mutex> lock(g_mu);
+    st = device_state(&rc);
+  }
+  if (st == nullptr) return rc;
+  if (st->status_host[0] != 0) return NEOGEMM_ERR_DEVICE_TIMEOUT;
+  // The waited time comes back through the same mapped page as the status record (words 8..9).
+  unsigned long long* waited_host = reinterpret_cast<unsigned long long*>(st->status_host + 8);
+  unsigned long long* waited_dev = reinterpret_cast<unsigned long long*>(st->status_dev + 8);
+  *waited_host = 0;
+  GemmParams params;
+  std::memset(&params, 0, sizeof(params));
+  params.status = st->status_dev;
+  wait_expiry_selftest_kernel<<<1, 32>>>(params, static_cast<unsigned long long>(limit_us) * 1000ull,
+                                         waited_dev);
+  if (cudaGetLastError() != cudaSuccess) return NEOGEMM_ERR_LAUNCH;
+  if (cudaDeviceSynchronize() != cudaSuccess) {
+    cudaGetLastError();
+    return NEOGEMM_ERR_CUDA;
+  }
+  if (waited_ns_out != nullptr) *waited_ns_out = *waited_host;
+  return NEOGEMM_OK;
+}
+
 int neogemm_version(void) { return 100; }
 
 int neogemm_debug_plan(int64_t M, int64_t N, int64_t K, int64_t ldc, int c_col_major, int sm_count,

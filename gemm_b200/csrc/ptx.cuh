@@ -162,7 +162,8 @@ constexpr uint64_t kWaitLimitNs = 2000ull * 1000ull * 1000ull;  // 2 s
 // (a word in shared memory).  The caller records the error and leaves its loop.
 template <bool kClusterScope = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
-                                          const volatile int* abort_flag, uint32_t hint_ns = 0) {
+                                          const volatile int* abort_flag, uint32_t hint_ns = 0,
+                                          uint64_t limit_ns = kWaitLimitNs) {
   auto test = [&]() -> bool {
     if (kClusterScope) return mbar_try_wait_cluster(bar, parity);
     return hint_ns ? mbar_try_wait_hint(bar, parity, hint_ns) : mbar_try_wait(bar, parity);
@@ -177,7 +178,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
       if (test()) return true;
     }
     if (*abort_flag != 0) return false;
-    if (globaltimer_ns() - t0 > kWaitLimitNs) return false;
+    if (globaltimer_ns() - t0 > limit_ns) return false;
   }
 }
 

@@ -196,6 +196,16 @@ int neogemm_set_phase_timers(void* device_buffer, size_t bytes);
 int neogemm_debug_plan(int64_t M, int64_t N, int64_t K, int64_t ldc, int c_col_major, int sm_count,
                        int* plan_out, int* segments, int max_segments);
 
+/* Self-test of the bounded device-side waits.  Launches one warp that waits, for at most
+ * `limit_us` microseconds (1..100000), on a barrier nothing will ever complete.  The warp must
+ * give up when the limit expires, record the error exactly as the GEMM's roles do (code 4, CTA 0,
+ * segment -1) and exit normally: afterwards neogemm_device_status() shows that record, every
+ * neogemm_bf16_nt* call returns NEOGEMM_ERR_DEVICE_TIMEOUT, and neogemm_clear_device_status()
+ * makes the library usable again - the CUDA context is unaffected throughout.  `waited_ns_out`
+ * (nullable) receives the time the warp actually waited.  Synchronous.  The reference has no
+ * error path to test (nemgemmV03.cu:387-390 prints cudaGetLastError). */
+int neogemm_debug_wait_expiry(unsigned int limit_us, unsigned long long* waited_ns_out);
+
 /* Library version, e.g. 100 = 1.0.0. */
 int neogemm_version(void);
 

@@ -267,3 +267,27 @@ def test_dynamic_tail_pool(case):
             ops.set_tuning(key, -1)
     torch.cuda.synchronize()
     assert ops.device_status()[0] == 0
+
+
+def test_bounded_wait_expires_into_an_error_code_and_the_library_recovers():
+    # Failure detection without a fault: a wait on a barrier nothing completes must run out,
+    # leave an error record, make later launches fail loudly - and clearing the record must bring
+    # everything back, on the same CUDA context.
+    import ctypes
+    from gemm_b200._lib import lib
+    lib.neogemm_debug_wait_expiry.restype = ctypes.c_int
+    lib.neogemm_debug_wait_expiry.argtypes = [ctypes.c_uint, ctypes.POINTER(ctypes.c_ulonglong)]
+    torch.cuda.synchronize()
+    assert ops.device_status()[0] == 0
+    waited = ctypes.c_ulonglong(0)
+    assert lib.neogemm_debug_wait_expiry(2000, ctypes.byref(waited)) == 0      # 2 ms limit
+    assert 2_000_000 <= waited.value < 50_000_000, waited.value
+    code, cta, segment, aux = ops.device_status()
+    assert (code, cta, segment, aux) == (4, 0, -1, -1)
+    A, B = make_problem(128, 128, 64, seed=1)
+    with pytest.raises(ops.NeoGemmError) as e:
+        ops.matmul(A.cuda(), B.cuda())
+    assert e.value.code == 5            # NEOGEMM_ERR_DEVICE_TIMEOUT: sticky until cleared
+    ops.clear_device_status()
+    assert ops.device_status() == (0, 0, 0, 0)
+    run_case(128, 128, 64)              # same context, same library: works again
