@@ -410,10 +410,10 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
       // Dynamic tail pool: with enough K, the last 16 or 32 k-blocks of every tile are left out
       // of the static ranges and claimed at run time in pieces of 16 (tuning key 4: 0 = off).
       int static_kb = p.num_k_blocks;
-      // Measured on the decode shapes: one piece per tile pays for 16 and 32 output columns
-      // (2 % faster at M=16); for wider tiles the extra partial round trips cost more than the
-      // balancing gains.
-      const int want = ov.tuning[4] >= 0 ? ov.tuning[4] : (block_n <= 32 ? kDefaultDynPieces : 0);
+      // Measured on the decode shapes: one piece per tile pays for 16 output columns (2 % faster
+      // at M=16); from 32 columns on the extra partial round trips cost more than the balancing
+      // gains (M=32: 78.8 us without, 83.2 us with).
+      const int want = ov.tuning[4] >= 0 ? ov.tuning[4] : (block_n <= 16 ? kDefaultDynPieces : 0);
       if (want > 0 && p.num_k_blocks >= 64 && cta_group == 1 && allow_hybrid) {
         p.dyn_ppt = std::min(want, 4);
         p.dyn_piece_kb = kDynPieceKBlocks;

@@ -79,9 +79,9 @@ def test_decode_shapes_use_swapped_stream_k(M):
     assert (p["swap"], p["stream_k"], p["cta_group"]) == (1, 1, 1)
     assert p["block_n"] == M and p["Md"] == 28672 and p["tiles"] == 224 and p["ctas"] == 148
     check_cover(p, segs)
-    # For M <= 32 the last 16 k-blocks of every tile are the dynamic tail pool: fixed pieces
+    # For M <= 16 the last 16 k-blocks of every tile are the dynamic tail pool: fixed pieces
     # claimed at run time.  The rest is cut into equal static ranges.
-    ppt = 1 if M <= 32 else 0
+    ppt = 1 if M <= 16 else 0
     static_kb = 128 - 16 * ppt
     pieces = [s for s in segs if s[2] >= static_kb]
     static = [s for s in segs if s[2] < static_kb]
