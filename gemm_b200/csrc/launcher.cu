@@ -333,7 +333,7 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
       const int rest = static_cast<int>(tiles % workers);
       double waves = static_cast<double>(tiles / workers);
       if (rest > 0) {
-        const int cut = allow_hybrid && ov.stream_k != 0 && c.halves == 1
+        const int cut = allow_hybrid && ov.stream_k != 0 && c.halves == 1 && tiles >= workers
             ? hybrid_splits(rest, static_cast<int>(workers), static_cast<int>((K + 63) / 64)) : 0;
         waves += cut > 0 ? 1.0 / cut + 0.05 : 1.0;
       }
@@ -384,12 +384,26 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
   bool stream_k = false;
   int sk_first = 0, sk_splits = 0;
   if (epi == kEpiDirect) {
-    stream_k = (block_n <= 128) && (p.num_k_blocks >= 8) && (p.num_tiles % workers_max != 0) &&
-               (p.num_tiles < 8 * workers_max);
-    if (ov.stream_k >= 0) stream_k = (ov.stream_k != 0);
+    if (p.num_tiles < workers) {
+      // Fewer tiles than SMs: cut every tile into the same few k-chunks, one per CTA.  Few
+      // contributors per tile keep the closing reduction short (a contiguous cut of such a
+      // small unit space would give each tile five or more).
+      sk_splits = ov.stream_k != 0 ? hybrid_splits(p.num_tiles, workers, p.num_k_blocks) : 0;
+      stream_k = sk_splits > 0;
+      if (ov.stream_k > 0 && !stream_k) stream_k = true;   // forced: contiguous ranges
+    } else {
+      // More tiles than SMs but not a whole number of waves (the decode shapes: 224 tiles on
+      // 148 SMs): equal contiguous ranges, provided every CTA keeps a long enough run.
+      const int64_t per_cta = static_cast<int64_t>(p.num_tiles) * p.num_k_blocks / workers;
+      stream_k = (block_n <= 128) && (per_cta >= 32) && (p.num_tiles % workers != 0) &&
+                 (p.num_tiles < 8 * workers);
+      if (ov.stream_k >= 0) stream_k = (ov.stream_k != 0);
+    }
   } else {
+    // Only behind at least one whole wave: the cut tiles are done first, and their closing
+    // reduction then hides under the whole tiles that follow.
     const int rest = p.num_tiles % workers;
-    sk_splits = allow_hybrid && ov.stream_k != 0 && p.halves == 1
+    sk_splits = allow_hybrid && ov.stream_k != 0 && p.halves == 1 && p.num_tiles >= workers
         ? hybrid_splits(rest, workers, p.num_k_blocks) : 0;
     stream_k = sk_splits > 0;
     sk_first = p.num_tiles - rest;
@@ -406,6 +420,7 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
   if (stream_k) {
     if (sk_splits > 0) {
       p.max_contrib = sk_splits;
+      if (sk_first == 0) workers = std::min(workers, sk_tiles * sk_splits);   // one chunk per CTA
     } else {
       // Dynamic tail pool: with enough K, the last 16 or 32 k-blocks of every tile are left out
       // of the static ranges and claimed at run time in pieces of 16 (tuning key 4: 0 = off).
