@@ -35,6 +35,10 @@ constexpr size_t kCounterRegionBytes = 256 * 1024;
 constexpr int kDefaultTuning[3] = {0, 2000, 0};
 // Throughput assumed for the 256 x 512 pair tile when ranking kernels (TFLOP/s at 8192^3).
 constexpr double kWideTileSpeed = 1650.0;
+// Microseconds the two-half tile spends handing its accumulators over between tiles, and the
+// time the store epilogue of one tile takes (both measured with the phase timers).
+constexpr double kHandOverUs = 3.5;
+constexpr double kEpilogueUs = 3.0;
 // k-blocks per dynamically claimed piece of the stream-K tail pool.
 constexpr int kDynPieceKBlocks = 16;
 // Row chunks the host entry point cuts the uploaded operand into (one product launch each).
@@ -269,11 +273,12 @@ int round_block_n(int64_t n) {
 
 // Into how many equal k-chunks the tiles of a last wave of `rest` tiles (of `workers`) are cut so
 // that every worker takes at most one chunk; 0 = leave the wave whole (it is more than half full,
-// or K is too short: a chunk must keep at least 8 k-blocks).
-int hybrid_splits(int rest, int workers, int num_k_blocks) {
+// or K is too short: a chunk must keep at least `min_chunk` k-blocks - 8 for the skinny kernels,
+// 16 for the large tiles, whose closing reduction of a cut tile is worth about that much work).
+int hybrid_splits(int rest, int workers, int num_k_blocks, int min_chunk = 8) {
   if (rest <= 0) return 0;
   int splits = workers / rest;            // k-chunks per tile so that every worker gets <= 1
-  splits = std::min(splits, num_k_blocks / 8);
+  splits = std::min(splits, num_k_blocks / min_chunk);
   return splits >= 2 ? std::min(splits, 8) : 0;
 }
 
@@ -334,10 +339,18 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
       double waves = static_cast<double>(tiles / workers);
       if (rest > 0) {
         const int cut = allow_hybrid && ov.stream_k != 0 && c.halves == 1 && tiles >= workers
-            ? hybrid_splits(rest, static_cast<int>(workers), static_cast<int>((K + 63) / 64)) : 0;
+            ? hybrid_splits(rest, static_cast<int>(workers), static_cast<int>((K + 63) / 64), 16)
+            : 0;
         waves += cut > 0 ? 1.0 / cut + 0.05 : 1.0;
       }
-      const double cost = waves * 128.0 * static_cast<double>(tile_n) / c.speed;
+      // Time of one tile on one worker at that kernel's throughput, in microseconds, plus what
+      // the epilogue adds: the two-half tile exposes the hand-over between tiles (no second
+      // accumulator), the others hide the epilogue unless the main loop is shorter than it.
+      const double workers_full = std::max(1, sm_count / c.cta_group);
+      const double t_main = 2.0 * static_cast<double>(tm) * static_cast<double>(tile_n) *
+                            static_cast<double>(K) / (c.speed * 1e6 / workers_full);
+      const double t_tile = (c.halves == 2) ? t_main + kHandOverUs : std::max(t_main, kEpilogueUs);
+      const double cost = waves * t_tile;
       if (best == 0.0 || cost < best) {
         best = cost;
         best_group = c.cta_group;
@@ -404,7 +417,7 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
     // reduction then hides under the whole tiles that follow.
     const int rest = p.num_tiles % workers;
     sk_splits = allow_hybrid && ov.stream_k != 0 && p.halves == 1 && p.num_tiles >= workers
-        ? hybrid_splits(rest, workers, p.num_k_blocks) : 0;
+        ? hybrid_splits(rest, workers, p.num_k_blocks, 16) : 0;
     stream_k = sk_splits > 0;
     sk_first = p.num_tiles - rest;
   }

@@ -47,7 +47,7 @@ def test_pair_kernel_is_deterministic():
 def test_cut_last_wave_on_every_tma_store_kernel(cta_group, block_n):
     # Force the stream-K treatment of the last, partly filled wave (ragged shape, several waves).
     ov = dict(cta_group=cta_group, block_n=block_n, swap=0, stream_k=1)
-    stats, cfg = run_case(3000, 5000, 1024, override=ov)
+    stats, cfg = run_case(3000, 5000, 2048, override=ov)
     assert cfg["stream_k"] == 1 and cfg["cta_group"] == cta_group, cfg
     run_case(1000, 520, 2048, override=ov, col_major=True)
 
