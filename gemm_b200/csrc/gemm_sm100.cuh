@@ -876,32 +876,75 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
       if constexpr (Cfg::kEpiMode == kEpiTmaStore && Cfg::kNHalves == 2) {
         // Two-half tile: all 512 TMEM columns belong to this tile, so the next tile's MMAs wait
         // for this read-out.  Keep it free of anything slow: this warp's share (32 rows x 128
-        // columns of each half) is pulled into registers as packed bf16 - half 0, hand it back,
-        // half 1, hand it back - and only then goes through the staging buffer and the TMA
+        // columns of each half) is pulled into registers - half 0, hand it back, pack to bf16,
+        // half 1, hand it back, pack - and only then goes through the staging buffer and the TMA
         // stores, whose shared-memory read-out takes about a microsecond per box.
         const uint32_t buf = epi_base + (warp - 2) * Cfg::SMEM_EPI_WARP_BUF;
         const int my_row0 = row0 + quad * 32;
         uint32_t packed[2][64];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-#pragma unroll
-          for (int part = 0; part < 4; ++part) {
-            const int c = h * BLOCK_N + warp_set * (BLOCK_N / 2) + part * 32;
-            uint32_t r[32];
+          // Half 0 is what the next tile's first MMA waits for: its four loads are issued back to
+          // back and waited for once (128 raw registers, free at this point).  Half 1 goes in two
+          // batches of two loads, next to the 64 packed registers of half 0.
+          const uint32_t t_half = taddr + h * BLOCK_N + warp_set * (BLOCK_N / 2);
+          const int c_half = col0 + h * BLOCK_N + warp_set * (BLOCK_N / 2);
+          if (h == 0) {
+            uint32_t ra[32], rb[32], rc[32], rd[32];
             __syncwarp();
-            tmem_ld_32x32b_x32(taddr + c, r);
+            tmem_ld_32x32b_x32(t_half, ra);
+            tmem_ld_32x32b_x32(t_half + 32, rb);
+            tmem_ld_32x32b_x32(t_half + 64, rc);
+            tmem_ld_32x32b_x32(t_half + 96, rd);
             tmem_ld_wait();
-            if (p.fuse) fused_epilogue<32>(r, p, row0 + row_in_cta, col0 + c);
+            // The values sit in registers: tensor memory goes back before they are packed.
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+              if (kCtaGroup == 2) mbar_arrive_cluster(leader_tmem_empty);
+              else mbar_arrive(tmem_empty_bar);
+            }
+            if (p.fuse) {
+              fused_epilogue<32>(ra, p, row0 + row_in_cta, c_half);
+              fused_epilogue<32>(rb, p, row0 + row_in_cta, c_half + 32);
+              fused_epilogue<32>(rc, p, row0 + row_in_cta, c_half + 64);
+              fused_epilogue<32>(rd, p, row0 + row_in_cta, c_half + 96);
+            }
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
-              packed[h][part * 16 + j] =
-                  pack_bf16x2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
-          }
-          tcgen05_fence_before();
-          __syncwarp();
-          if (lane == 0) {
-            if (kCtaGroup == 2) mbar_arrive_cluster(leader_tmem_empty + 8 * h);
-            else mbar_arrive(tmem_empty_bar + 8 * h);
+            for (int j = 0; j < 16; ++j) {
+              packed[h][j] = pack_bf16x2(__uint_as_float(ra[2 * j]), __uint_as_float(ra[2 * j + 1]));
+              packed[h][16 + j] = pack_bf16x2(__uint_as_float(rb[2 * j]), __uint_as_float(rb[2 * j + 1]));
+              packed[h][32 + j] = pack_bf16x2(__uint_as_float(rc[2 * j]), __uint_as_float(rc[2 * j + 1]));
+              packed[h][48 + j] = pack_bf16x2(__uint_as_float(rd[2 * j]), __uint_as_float(rd[2 * j + 1]));
+            }
+          } else {
+#pragma unroll
+            for (int bt = 0; bt < 2; ++bt) {
+              uint32_t ra[32], rb[32];
+              __syncwarp();
+              tmem_ld_32x32b_x32(t_half + bt * 64, ra);
+              tmem_ld_32x32b_x32(t_half + bt * 64 + 32, rb);
+              tmem_ld_wait();
+              if (bt == 1) {
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                  if (kCtaGroup == 2) mbar_arrive_cluster(leader_tmem_empty + 8);
+                  else mbar_arrive(tmem_empty_bar + 8);
+                }
+              }
+              if (p.fuse) {
+                fused_epilogue<32>(ra, p, row0 + row_in_cta, c_half + bt * 64);
+                fused_epilogue<32>(rb, p, row0 + row_in_cta, c_half + bt * 64 + 32);
+              }
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                packed[h][bt * 32 + j] =
+                    pack_bf16x2(__uint_as_float(ra[2 * j]), __uint_as_float(ra[2 * j + 1]));
+                packed[h][bt * 32 + 16 + j] =
+                    pack_bf16x2(__uint_as_float(rb[2 * j]), __uint_as_float(rb[2 * j + 1]));
+              }
+            }
           }
         }
         released = true;
