@@ -57,6 +57,7 @@ struct GemmParams {
                              // bit 4: Y loads evict-last (0 = no hints)
   int epi_wait_hint_ns;      // suspend hint of the epilogue's wait for an accumulator (0 = none)
   int main_wait_hint_ns;     // suspend hint of the producer's and the MMA warp's ring waits
+  int wide_prologue;         // two-half tiles: k-blocks issued for half 0 alone at a tile's start
   // Direct epilogue / split partials.
   __nv_bfloat16* out;
   long long out_stride_r, out_stride_c;
@@ -675,13 +676,13 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
           // little later, so the first k-blocks (as many as the ring holds minus one) are issued
           // for half 0 alone, then, once half 1 is back, for half 1 - which also releases their
           // ring slots.  The tensor pipe restarts as soon as half 0 is drained.
-          const int pro = min(kStages - 1, seg.kb_count);
+          const int pro = min(min(kStages - 1, max(p.wide_prologue, 1)), seg.kb_count);
 #pragma unroll 1
           for (int h = 0; h < 2 && ok; ++h) {
             tmem_timer.begin();
             const bool drained = __all_sync(
                 0xffffffffu,
-                mbar_wait<kCtaGroup == 2>(tmem_empty_bar + 8 * h, acc_phase ^ 1, abort_flag));
+                mbar_wait<kCtaGroup == 2, true>(tmem_empty_bar + 8 * h, acc_phase ^ 1, abort_flag));
             tmem_timer.end();
             if (!drained) {
               if (lane == 0) report_error(p, abort_flag, kDevTimeoutMmaTmem, seg_idx, h);
@@ -727,7 +728,19 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
           if (!ok) break;
           kb_first = pro;
         }
+        // Two-half tiles: early notice to the epilogue warps of both CTAs a few k-blocks before the
+        // tile's last MMA is issued (they wake from a suspended wait, which can take microseconds,
+        // and then poll the accumulator barrier).
+        const int notice_kb = max(kb_first, seg.kb_count - 3);
+        bool noticed = false;
         for (int kb = kb_first; kb < seg.kb_count; ++kb) {
+          if (Cfg::kNHalves == 2 && kb == notice_kb) {
+            if (elect_one()) {
+              mbar_arrive(tmem_full_bar + 8);
+              if (kCtaGroup == 2) mbar_arrive_cluster(mapa_u32(tmem_full_bar + 8, 1));
+            }
+            noticed = true;
+          }
           wait_timer.begin();
           const bool got = __all_sync(0xffffffffu,
                                       mbar_wait(full_bar + 8 * stage, phase, abort_flag,
@@ -761,6 +774,10 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
         }
         if (!ok) break;
         if (elect_one()) {
+          if (Cfg::kNHalves == 2 && !noticed) {   // short tiles: the loop above did not run
+            mbar_arrive(tmem_full_bar + 8);
+            if (kCtaGroup == 2) mbar_arrive_cluster(mapa_u32(tmem_full_bar + 8, 1));
+          }
           if (kCtaGroup == 2) umma_commit_both_ctas(tmem_full_bar + 8 * acc);
           else umma_commit<1>(tmem_full_bar + 8 * acc);
         }
@@ -796,11 +813,24 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
     while (ok && it.next(seg, lane)) {
       const uint32_t acc = (Cfg::kNHalves == 1) ? (seg_idx & 1) : 0;
       const uint32_t acc_phase = (Cfg::kNHalves == 1) ? ((seg_idx >> 1) & 1) : (seg_idx & 1);
+      // Everything that does not need the accumulator is worked out before the wait: with a
+      // two-half tile the tensor pipe idles from the moment the barrier fires until this warp has
+      // read its share, and the index arithmetic alone was ~1500 cycles of that.
+      int tm, tn;
+      tile_coords(p, seg.tile, tm, tn);
+      const int row0 = tm * Cfg::TILE_M + static_cast<int>(cta_rank) * Cfg::BLOCK_M;
+      const int col0 = tn * Cfg::TILE_N;
+      const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + acc * Cfg::kAccumCols;
+      // Pin the values in registers here; otherwise the compiler sinks the arithmetic to its first
+      // use, which is behind the wait.
+      asm volatile("" ::"r"(row0), "r"(col0), "r"(taddr));
       wait_timer.begin();
       // One lane polls; the other 31 sleep at the shuffle instead of hammering the barrier.
       int got_i = 0;
+      // Two-half tiles sleep on the early notice (barrier slot 1, raised when the tile's last MMA
+      // has been issued) and then poll the real barrier from inside the read-out loop below.
       if (lane == 0)
-        got_i = mbar_wait(tmem_full_bar + 8 * acc, acc_phase, abort_flag,
+        got_i = mbar_wait(tmem_full_bar + 8 * (Cfg::kNHalves == 2 ? 1u : acc), acc_phase, abort_flag,
                           static_cast<uint32_t>(p.epi_wait_hint_ns)) ? 1 : 0;
       const bool got = __shfl_sync(0xffffffffu, got_i, 0) != 0;
       wait_timer.end();
@@ -809,11 +839,6 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
         break;
       }
       tcgen05_fence_after();
-      int tm, tn;
-      tile_coords(p, seg.tile, tm, tn);
-      const int row0 = tm * Cfg::TILE_M + static_cast<int>(cta_rank) * Cfg::BLOCK_M;
-      const int col0 = tn * Cfg::TILE_N;
-      const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + acc * Cfg::kAccumCols;
 
       // ---- stream-K: publish this segment's partial; the last arriver finishes the rows ----
       bool finish = true;
@@ -882,42 +907,73 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
         const uint32_t buf = epi_base + (warp - 2) * Cfg::SMEM_EPI_WARP_BUF;
         const int my_row0 = row0 + quad * 32;
         uint32_t packed[2][64];
+        {
+          // Half 0 is what the next tile's first MMA waits for.  Its four loads (128 raw
+          // registers, free at this point) run in a loop that starts at the early notice and
+          // tests the accumulator barrier once per turn: turns before the barrier fires read
+          // unfinished sums and are thrown away, but they keep this code and its registers hot,
+          // so that the turn which sees the barrier hands the half back ~300 cycles later.  A
+          // cold start (wake-up, instruction fetch, spills) cost 2000-3500 cycles per tile.
+          const uint32_t t_half = taddr + warp_set * (BLOCK_N / 2);
+          const int c_half = col0 + warp_set * (BLOCK_N / 2);
+          uint32_t ra[32], rb[32], rc[32], rd[32];
+          bool ready = false, expired = false;
+          uint32_t turns = 0;
+          uint64_t t_first = 0;
+#pragma unroll 1
+          for (;;) {
+            int r = 0;
+            if (lane == 0) r = mbar_test_wait(tmem_full_bar, acc_phase) ? 1 : 0;
+            ready = __shfl_sync(0xffffffffu, r, 0) != 0;
+            if (ready) {
+              tcgen05_fence_after();
+              tmem_ld_32x32b_x32(t_half, ra);
+              tmem_ld_32x32b_x32(t_half + 32, rb);
+              tmem_ld_32x32b_x32(t_half + 64, rc);
+              tmem_ld_32x32b_x32(t_half + 96, rd);
+              tmem_ld_wait();
+              break;
+            }
+            if ((++turns & 63u) == 0) {
+              int stop = 0;
+              if (lane == 0) {
+                const uint64_t now = globaltimer_ns();
+                if (t_first == 0) t_first = now;
+                stop = (*abort_flag != 0 || now - t_first > kWaitLimitNs) ? 1 : 0;
+              }
+              if (__shfl_sync(0xffffffffu, stop, 0) != 0) { expired = true; break; }
+            }
+          }
+          if (expired) {
+            if (lane == 0) report_error(p, abort_flag, kDevTimeoutEpilogue, seg_idx, 0);
+            break;
+          }
+          // The values sit in registers: tensor memory goes back before they are packed.
+          tcgen05_fence_before();
+          __syncwarp();
+          if (lane == 0) {
+            if (kCtaGroup == 2) mbar_arrive_cluster(leader_tmem_empty);
+            else mbar_arrive(tmem_empty_bar);
+          }
+          if (p.fuse) {
+            fused_epilogue<32>(ra, p, row0 + row_in_cta, c_half);
+            fused_epilogue<32>(rb, p, row0 + row_in_cta, c_half + 32);
+            fused_epilogue<32>(rc, p, row0 + row_in_cta, c_half + 64);
+            fused_epilogue<32>(rd, p, row0 + row_in_cta, c_half + 96);
+          }
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          // Half 0 is what the next tile's first MMA waits for: its four loads are issued back to
-          // back and waited for once (128 raw registers, free at this point).  Half 1 goes in two
-          // batches of two loads, next to the 64 packed registers of half 0.
+          for (int j = 0; j < 16; ++j) {
+            packed[0][j] = pack_bf16x2(__uint_as_float(ra[2 * j]), __uint_as_float(ra[2 * j + 1]));
+            packed[0][16 + j] = pack_bf16x2(__uint_as_float(rb[2 * j]), __uint_as_float(rb[2 * j + 1]));
+            packed[0][32 + j] = pack_bf16x2(__uint_as_float(rc[2 * j]), __uint_as_float(rc[2 * j + 1]));
+            packed[0][48 + j] = pack_bf16x2(__uint_as_float(rd[2 * j]), __uint_as_float(rd[2 * j + 1]));
+          }
+        }
+        {
+          constexpr int h = 1;
           const uint32_t t_half = taddr + h * BLOCK_N + warp_set * (BLOCK_N / 2);
           const int c_half = col0 + h * BLOCK_N + warp_set * (BLOCK_N / 2);
-          if (h == 0) {
-            uint32_t ra[32], rb[32], rc[32], rd[32];
-            __syncwarp();
-            tmem_ld_32x32b_x32(t_half, ra);
-            tmem_ld_32x32b_x32(t_half + 32, rb);
-            tmem_ld_32x32b_x32(t_half + 64, rc);
-            tmem_ld_32x32b_x32(t_half + 96, rd);
-            tmem_ld_wait();
-            // The values sit in registers: tensor memory goes back before they are packed.
-            tcgen05_fence_before();
-            __syncwarp();
-            if (lane == 0) {
-              if (kCtaGroup == 2) mbar_arrive_cluster(leader_tmem_empty);
-              else mbar_arrive(tmem_empty_bar);
-            }
-            if (p.fuse) {
-              fused_epilogue<32>(ra, p, row0 + row_in_cta, c_half);
-              fused_epilogue<32>(rb, p, row0 + row_in_cta, c_half + 32);
-              fused_epilogue<32>(rc, p, row0 + row_in_cta, c_half + 64);
-              fused_epilogue<32>(rd, p, row0 + row_in_cta, c_half + 96);
-            }
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              packed[h][j] = pack_bf16x2(__uint_as_float(ra[2 * j]), __uint_as_float(ra[2 * j + 1]));
-              packed[h][16 + j] = pack_bf16x2(__uint_as_float(rb[2 * j]), __uint_as_float(rb[2 * j + 1]));
-              packed[h][32 + j] = pack_bf16x2(__uint_as_float(rc[2 * j]), __uint_as_float(rc[2 * j + 1]));
-              packed[h][48 + j] = pack_bf16x2(__uint_as_float(rd[2 * j]), __uint_as_float(rd[2 * j + 1]));
-            }
-          } else {
+          {
 #pragma unroll
             for (int bt = 0; bt < 2; ++bt) {
               uint32_t ra[32], rb[32];
@@ -1162,7 +1218,9 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
       ++seg_idx;
     }
     if (it.failed && lane == 0) report_error(p, abort_flag, kDevTimeoutScheduler, seg_idx, 2);
-    if (Cfg::kEpiMode == kEpiTmaStore && lane == 0) tma_store_wait_all<0>();
+    // Shared memory must outlive the stores' reads of it; their writes to global memory are
+    // complete when the grid is, which is all a later kernel or copy can observe.
+    if (Cfg::kEpiMode == kEpiTmaStore && lane == 0) tma_store_wait_read<0>();
     loop_timer.end();
     loop_timer.stamp(11);
     loop_timer.flush(6);

@@ -33,6 +33,11 @@ constexpr int kMaxDevices = 64;
 constexpr size_t kCounterRegionBytes = 256 * 1024;
 // Defaults of the neogemm_set_tuning keys: L2 hint mask, epilogue wait hint (ns), ring wait hint (ns).
 constexpr int kDefaultTuning[3] = {0, 2000, 0};
+// Two-half tiles: k-blocks issued for half 0 alone when a tile starts.  Half 1 comes back from the
+// epilogue ~500 cycles after half 0, so one k-block (512 cycles of tensor work) covers it, and the
+// first ring slot is released - and refilled - two k-blocks earlier than with three (8192^3: 924 k
+// cycles in the MMA loop against 926 k with two and 928 k with three).
+constexpr int kDefaultWidePrologue = 1;
 // Throughput assumed for the 256 x 512 pair tile when ranking kernels (TFLOP/s at 8192^3).
 constexpr double kWideTileSpeed = 1650.0;
 // Microseconds the two-half tile spends handing its accumulators over between tiles, and the
@@ -121,7 +126,7 @@ bool g_encode_looked_up = false;
 
 struct Override {
   int cta_group = -1, block_n = -1, swap = -1, stream_k = -1, group_m = -1, max_ctas = -1;
-  int tuning[6] = {-1, -1, -1, -1, -1, -1};   // see neogemm_set_tuning
+  int tuning[7] = {-1, -1, -1, -1, -1, -1, -1};   // see neogemm_set_tuning
 };
 thread_local Override t_override;
 thread_local int t_last_config[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -622,6 +627,7 @@ int gemm_device(const void* A, const void* B, void* C, int64_t M, int64_t N, int
   params.l2_hints = t_override.tuning[0] >= 0 ? t_override.tuning[0] : default_hints;
   params.epi_wait_hint_ns = t_override.tuning[1] >= 0 ? t_override.tuning[1] : kDefaultTuning[1];
   params.main_wait_hint_ns = t_override.tuning[2] >= 0 ? t_override.tuning[2] : kDefaultTuning[2];
+  params.wide_prologue = t_override.tuning[6] >= 0 ? t_override.tuning[6] : kDefaultWidePrologue;
   params.out = static_cast<__nv_bfloat16*>(C);
   params.out_stride_r = plan.swap ? 1 : ldc;
   params.out_stride_c = plan.swap ? ldc : 1;
@@ -930,7 +936,7 @@ int neogemm_set_phase_timers(void* device_buffer, size_t bytes) {
 }
 
 int neogemm_set_tuning(int key, int value) {
-  if (key < 0 || key > 5 || (key == 5 && value > 3) || value > 1000000 || (key == 0 && value > 31) || (key == 3 && value > 1) ||
+  if (key < 0 || key > 6 || (key == 6 && (value == 0 || value > 3)) || (key == 5 && value > 3) || value > 1000000 || (key == 0 && value > 31) || (key == 3 && value > 1) ||
       (key == 4 && value > 4))
     return NEOGEMM_ERR_BAD_ARG;
   t_override.tuning[key] = value;

@@ -142,6 +142,35 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity
   return ok != 0;
 }
 
+// Non-blocking test of a phase (no suspend): for loops that have something else to do per turn.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+__device__ __forceinline__ bool mbar_test_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Same, with cluster-scope acquire: used where the completing arrive came from the peer CTA.
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -163,11 +192,14 @@ constexpr uint64_t kWaitLimitNs = 2000ull * 1000ull * 1000ull;  // 2 s
 
 // Bounded wait.  Returns false if the limit expired or another role already raised `*abort_flag`
 // (a word in shared memory).  The caller records the error and leaves its loop.
-template <bool kClusterScope = false>
+template <bool kClusterScope = false, bool kSpin = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
                                           const volatile int* abort_flag, uint32_t hint_ns = 0,
                                           uint64_t limit_ns = kWaitLimitNs) {
   auto test = [&]() -> bool {
+    // kSpin: non-blocking tests, for short waits on a critical path (a suspended try_wait can
+    // come back hundreds of cycles after the phase completed).
+    if (kSpin) return kClusterScope ? mbar_test_wait_cluster(bar, parity) : mbar_test_wait(bar, parity);
     if (kClusterScope) return mbar_try_wait_cluster(bar, parity);
     return hint_ns ? mbar_try_wait_hint(bar, parity, hint_ns) : mbar_try_wait(bar, parity);
   };
@@ -275,12 +307,6 @@ __device__ __forceinline__ void tma_store_commit() {
 template <int N>
 __device__ __forceinline__ void tma_store_wait_read() {
   asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
-}
-
-// Wait until at most N store groups are incomplete (writes performed).
-template <int N>
-__device__ __forceinline__ void tma_store_wait_all() {
-  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
 
 // ----------------------------------------------------------------------------------------------

@@ -168,6 +168,8 @@ int neogemm_set_override(int cta_group, int block_n, int swap, int stream_k, int
  *   key 5: L2 promotion of the TMA loads: 0 none, 1 64 B, 2 128 B, 3 256 B (default).
  *   key 4: pieces (of 16 k-blocks) per tile that the stream-K schedule of skinny shapes leaves to
  *          be claimed at run time instead of assigning them statically (0 = none, up to 4).
+ *   key 6: two-half tiles: k-blocks (1..3) issued for the first half alone at the start of a tile,
+ *          while the epilogue still reads the second half of the previous tile.
  * No counterpart in the reference (its maps only set L2 promotion, nemgemmV03.cu:52). */
 int neogemm_set_tuning(int key, int value);
 

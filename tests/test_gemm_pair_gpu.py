@@ -81,6 +81,17 @@ def test_wide_pair_tile_ragged(shape):
     run_case(*shape, tuning={"wide_tile": 1}, col_major=True)
 
 
+@pytest.mark.parametrize("prologue", [1, 2, 3])
+@pytest.mark.parametrize("shape", [(2048, 4096, 64), (2048, 4096, 128), (2104, 4104, 192),
+                                   (2048, 4096, 320), (4096, 8192, 2048)])
+def test_wide_pair_tile_hand_over(shape, prologue):
+    # Several tiles per CTA pair, so every hand-over path runs: tiles of one to a few k-blocks
+    # (shorter than the half-0 prologue and than the early notice to the epilogue warps) and
+    # long ones, with each prologue length.
+    stats, cfg = run_case(*shape, tuning={"wide_tile": 1, "wide_tile_prologue": prologue})
+    assert cfg["block_n"] == 512 and cfg["cta_group"] == 2, cfg
+
+
 def test_wide_pair_tile_is_deterministic_and_never_wide_when_switched_off():
     from gemm_b200.inputs import make_problem
     A, B = make_problem(2048, 4096, 1024, seed=14)
