@@ -135,6 +135,11 @@ struct GemmConfig {
       : (2 * BLOCK_N <= 32) ? 32 : (2 * BLOCK_N <= 64) ? 64 : (2 * BLOCK_N <= 128) ? 128
       : (2 * BLOCK_N <= 256) ? 256 : 512;
   static constexpr int kThreads = 64 + 32 * kEpiWarps;   // TMA warp, MMA warp, epilogue warps
+  // A configuration that needs less than half of an SM's shared memory is built so that two of
+  // its CTAs can share an SM (registers capped accordingly); both then hold a slice of tensor
+  // memory at once, which is safe as long as two slices fit.
+  static constexpr int kCtasPerSm = (SMEM_TOTAL <= 115712) ? 2 : 1;
+  static_assert(kCtasPerSm == 1 || kTmemCols <= 256, "two resident CTAs must both fit in TMEM");
   static_assert(BLOCK_N % 16 == 0 && BLOCK_N >= 16 && BLOCK_N <= 256, "UMMA N");
   static_assert(kNHalves == 1 || (kNHalves == 2 && BLOCK_N == 256 && kEpiMode == kEpiTmaStore),
                 "the two-half tile fills tensor memory: 2 x 256 fp32 columns, TMA-store epilogue");
@@ -482,7 +487,7 @@ __device__ __forceinline__ void sum_partials(uint32_t (&r)[kN], const float* col
 }
 
 template <class Cfg>
-__global__ void __launch_bounds__(Cfg::kThreads, 1)
+__global__ void __launch_bounds__(Cfg::kThreads, Cfg::kCtasPerSm)
 gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
                     const __grid_constant__ CUtensorMap tmap_y,
                     const __grid_constant__ CUtensorMap tmap_d,

@@ -44,6 +44,11 @@ constexpr double kWideTileSpeed = 1650.0;
 // time the store epilogue of one tile takes (both measured with the phase timers).
 constexpr double kHandOverUs = 3.5;
 constexpr double kEpilogueUs = 3.0;
+// Widest tile (columns) that has a half-size-ring kernel for two CTAs per SM, and the widest for
+// which the launcher picks it on its own: at 64 columns only three ring stages fit and stream-K
+// over full-size rings is faster (M=64 decode: 83.6 us against 84.5 us).
+constexpr int kResidentMaxColumns = 64;
+constexpr int kResidentAutoColumns = 32;
 // k-blocks per dynamically claimed piece of the stream-K tail pool.
 constexpr int kDynPieceKBlocks = 16;
 // Row chunks the host entry point cuts the uploaded operand into (one product launch each).
@@ -56,6 +61,7 @@ constexpr int kDefaultDynPieces = 1;
 // ------------------------------------------------------------------------------------------
 struct KernelEntry {
   int cta_group, block_n, stages, epi, halves;
+  int per_sm;   // CTAs of this kernel that fit on one SM together (1 or 2)
   const void* fn;
   int smem_bytes;
   int tmem_cols;
@@ -65,7 +71,7 @@ struct KernelEntry {
 template <class Cfg>
 KernelEntry make_entry() {
   return KernelEntry{Cfg::kCtaGroup, Cfg::BLOCK_N, Cfg::kStages, Cfg::kEpiMode, Cfg::kNHalves,
-                     reinterpret_cast<const void*>(&gemm_bf16_nt_kernel<Cfg>), Cfg::SMEM_TOTAL,
+                     Cfg::kCtasPerSm, reinterpret_cast<const void*>(&gemm_bf16_nt_kernel<Cfg>), Cfg::SMEM_TOTAL,
                      Cfg::kTmemCols, Cfg::kThreads};
 }
 
@@ -82,17 +88,23 @@ const KernelEntry* kernel_table(int* count) {
       make_entry<GemmConfig<1, 64, 8, kEpiDirect>>(),
       make_entry<GemmConfig<1, 32, 10, kEpiDirect>>(),
       make_entry<GemmConfig<1, 16, 12, kEpiDirect>>(),
+      // Half-size rings: two CTAs per SM, one whole tile each (skinny shapes with between one and
+      // two tiles per SM, which then need no cut tiles and no closing reduction).
+      make_entry<GemmConfig<1, 64, 3, kEpiDirect>>(),
+      make_entry<GemmConfig<1, 32, 5, kEpiDirect>>(),
+      make_entry<GemmConfig<1, 16, 5, kEpiDirect>>(),
   };
   *count = static_cast<int>(sizeof(table) / sizeof(table[0]));
   return table;
 }
 
-const KernelEntry* find_kernel(int cta_group, int block_n, int epi, int halves, int* index) {
+const KernelEntry* find_kernel(int cta_group, int block_n, int epi, int halves, int per_sm,
+                               int* index) {
   int n;
   const KernelEntry* t = kernel_table(&n);
   for (int i = 0; i < n; ++i) {
     if (t[i].cta_group == cta_group && t[i].block_n == block_n && t[i].epi == epi &&
-        t[i].halves == halves) {
+        t[i].halves == halves && t[i].per_sm == per_sm) {
       if (index) *index = i;
       return &t[i];
     }
@@ -126,7 +138,7 @@ bool g_encode_looked_up = false;
 
 struct Override {
   int cta_group = -1, block_n = -1, swap = -1, stream_k = -1, group_m = -1, max_ctas = -1;
-  int tuning[7] = {-1, -1, -1, -1, -1, -1, -1};   // see neogemm_set_tuning
+  int tuning[8] = {-1, -1, -1, -1, -1, -1, -1, -1};   // see neogemm_set_tuning
 };
 thread_local Override t_override;
 thread_local int t_last_config[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -254,6 +266,7 @@ struct Plan {
   bool swap = false;        // X = the operand that indexes output COLUMNS of the stored matrix
   int cta_group = 1, block_n = 256, epi = kEpiTmaStore;
   int halves = 1;           // 2: 256 x 512 pair tile (two UMMA-N halves sharing X)
+  int per_sm = 1;           // 2: half-size rings, two CTAs per SM, one whole tile each
   bool stream_k = false;
   int sk_first_tile = 0;    // tiles below are handed out round-robin, tiles from here on are cut
   int sk_splits = 0;        // > 0: uniform k-chunks per cut tile (large kernels)
@@ -370,15 +383,30 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
   p.block_n = block_n;
   p.cta_group = cta_group;
   p.epi = epi;
-  p.kernel = find_kernel(cta_group, block_n, epi, p.halves, &p.kernel_index);
-  if (p.kernel == nullptr) return NEOGEMM_ERR_UNSUPPORTED;
-
   const int tile_m = 128 * cta_group;
   p.num_m_tiles = static_cast<int>((md + tile_m - 1) / tile_m);
   const int tile_n = block_n * p.halves;
   p.num_n_tiles = static_cast<int>((nd + tile_n - 1) / tile_n);
   const int64_t tiles = static_cast<int64_t>(p.num_m_tiles) * p.num_n_tiles;
   if (tiles > 0x3fffffffll) return NEOGEMM_ERR_UNSUPPORTED;
+
+  // Skinny shapes with more tiles than SMs but at most two per SM (decode: 224 tiles of 128 rows
+  // on 148 SMs) run as ONE wave of whole tiles, two CTAs per SM with half-size rings: every CTA
+  // streams one tile's rows over all of K, nothing is cut, nothing has to be summed at the end.
+  // cuBLAS' choice for M=16 has the same shape (112 whole tiles of 256 rows, no split-K).
+  // Measured (CUDA-graph replays, M x 28672 x 8192): M=16 78.7 -> 74.7 us, M=32 83.4 -> 77.6 us.
+  // Tuning key 7: -1 auto, 0 never, 1 whenever the kernel exists and the tiles fit.
+  int per_sm = 1;
+  if (epi == kEpiDirect && cta_group == 1 && ov.tuning[7] != 0 && ov.stream_k <= 0 &&
+      ov.max_ctas <= 0 && tiles <= 2ll * sm_count && (K + 63) / 64 >= 16) {
+    const bool forced = (ov.tuning[7] == 1) && block_n <= kResidentMaxColumns;
+    const bool automatic = (ov.tuning[7] < 0) && block_n <= kResidentAutoColumns && tiles > sm_count;
+    if (forced || automatic) per_sm = 2;
+  }
+  p.per_sm = per_sm;
+  p.kernel = find_kernel(cta_group, block_n, epi, p.halves, per_sm, &p.kernel_index);
+  if (p.kernel == nullptr) return NEOGEMM_ERR_UNSUPPORTED;
+
   p.num_tiles = static_cast<int>(tiles);
   p.num_k_blocks = static_cast<int>((K + 63) / 64);
 
@@ -389,7 +417,7 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
   if (ov.group_m > 0) p.group_m = ov.group_m;
   p.group_m = std::max(1, std::min(p.group_m, p.num_m_tiles));
 
-  const int workers_max = std::max(1, sm_count / cta_group);
+  const int workers_max = std::max(1, per_sm * sm_count / cta_group);
   int workers = workers_max;
   if (ov.max_ctas > 0) workers = std::max(1, std::min(workers, ov.max_ctas / cta_group));
 
@@ -401,7 +429,9 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
   //    4096^3 is 3.46 waves of pair tiles).
   bool stream_k = false;
   int sk_first = 0, sk_splits = 0;
-  if (epi == kEpiDirect) {
+  if (per_sm == 2) {
+    // one whole tile per CTA, all resident at once
+  } else if (epi == kEpiDirect) {
     if (p.num_tiles < workers) {
       // Fewer tiles than SMs: cut every tile into the same few k-chunks, one per CTA.  Few
       // contributors per tile keep the closing reduction short (a contiguous cut of such a
@@ -936,7 +966,7 @@ int neogemm_set_phase_timers(void* device_buffer, size_t bytes) {
 }
 
 int neogemm_set_tuning(int key, int value) {
-  if (key < 0 || key > 6 || (key == 6 && (value == 0 || value > 3)) || (key == 5 && value > 3) || value > 1000000 || (key == 0 && value > 31) || (key == 3 && value > 1) ||
+  if (key < 0 || key > 7 || (key == 6 && (value == 0 || value > 3)) || (key == 7 && value > 1) || (key == 5 && value > 3) || value > 1000000 || (key == 0 && value > 31) || (key == 3 && value > 1) ||
       (key == 4 && value > 4))
     return NEOGEMM_ERR_BAD_ARG;
   t_override.tuning[key] = value;

@@ -170,6 +170,9 @@ int neogemm_set_override(int cta_group, int block_n, int swap, int stream_k, int
  *          be claimed at run time instead of assigning them statically (0 = none, up to 4).
  *   key 6: two-half tiles: k-blocks (1..3) issued for the first half alone at the start of a tile,
  *          while the epilogue still reads the second half of the previous tile.
+ *   key 7: skinny shapes with between one and two tiles per SM as ONE wave of whole tiles, two
+ *          CTAs per SM with half-size rings (no cut tiles, no closing sums): -1 chosen by the
+ *          launcher, 0 never, 1 whenever such a kernel exists and all tiles fit at once.
  * No counterpart in the reference (its maps only set L2 promotion, nemgemmV03.cu:52). */
 int neogemm_set_tuning(int key, int value);
 

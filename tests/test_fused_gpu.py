@@ -25,9 +25,10 @@ def reference(A, B, alpha, beta, c_old, bias, activation):
     return v
 
 
-CASES = [  # (M, N, K): pair kernel, cut last wave, single-CTA TMA store, direct, swapped stream-K
+CASES = [  # (M, N, K): pair kernel, cut last wave, single-CTA TMA store, direct, swapped stream-K,
+    # whole tiles two CTAs to an SM
     (2048, 2048, 512), (4096, 4096, 1024), (520, 776, 264), (257, 250, 128), (16, 3584, 2048),
-    (64, 28672, 1024),
+    (64, 28672, 1024), (24, 20000, 1024),
 ]
 
 

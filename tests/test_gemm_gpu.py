@@ -30,11 +30,38 @@ def test_config_8192_cube():
     run_case(8192, 8192, 8192)
 
 
-@pytest.mark.parametrize("M", [16, 64, 128])
+@pytest.mark.parametrize("M", [16, 32, 64, 128])
 def test_config_decode_shapes(M):
     stats, cfg = run_case(M, 28672, 8192)
-    assert cfg["swap"] == 1 and cfg["stream_k"] == 1, cfg
+    assert cfg["swap"] == 1, cfg
+    if M <= 32:   # one wave of 224 whole tiles, two CTAs to an SM
+        assert (cfg["stream_k"], cfg["ctas"], cfg["stages"]) == (0, 224, 5), cfg
+    else:         # stream-K over 148 CTAs
+        assert (cfg["stream_k"], cfg["ctas"]) == (1, 148), cfg
     run_case(M, 28672, 8192, col_major=True)
+
+
+@pytest.mark.parametrize("shape", [(16, 28672, 8192), (8, 19000, 1024), (24, 30000, 2048),
+                                   (64, 28672, 4096), (40, 20008, 1536), (1, 37000, 1024)])
+def test_two_ctas_per_sm_whole_tiles(shape):
+    # Half-size rings, every tile resident at once (forced, so that the 64-column kernel and
+    # shapes the launcher would not pick on its own run too); ragged rows and K, both layouts,
+    # and the stream-K plan of the same shape must give the same bits where no tile is cut
+    # differently - checked against the oracle, and launch to launch for determinism.
+    stats, cfg = run_case(*shape, tuning={"two_ctas_per_sm": 1})
+    assert cfg["stream_k"] == 0 and cfg["ctas"] == cfg["tiles"] and cfg["stages"] in (3, 5), cfg
+    run_case(*shape, tuning={"two_ctas_per_sm": 1}, col_major=True)
+    A, B = make_problem(*shape, seed=5)
+    dA, dB = A.cuda(), B.cuda()
+    ops.set_tuning("two_ctas_per_sm", 1)
+    try:
+        first = ops.matmul(dA, dB).clone()
+        for _ in range(4):
+            assert torch.equal(first.view(torch.int16), ops.matmul(dA, dB).view(torch.int16))
+    finally:
+        ops.set_tuning("two_ctas_per_sm", -1)
+    torch.cuda.synchronize()
+    assert ops.device_status()[0] == 0
 
 
 # ---- edges the reference cannot handle (it needs multiples of 64, nemgemmV03.cu:375) ----------
@@ -250,7 +277,9 @@ def test_dynamic_tail_pool(case):
     # The last k-blocks of every tile are claimed at run time; who computes them varies from
     # launch to launch, the bits must not.
     (M, N, K), pieces, ctas = case
-    tuning = {} if pieces is None else {"dynamic_pieces_per_tile": pieces}
+    tuning = {"two_ctas_per_sm": 0}
+    if pieces is not None:
+        tuning["dynamic_pieces_per_tile"] = pieces
     ov = dict(stream_k=1, swap=1, max_ctas=ctas) if ctas else None
     stats, cfg = run_case(M, N, K, tuning=tuning, override=ov)
     assert cfg["stream_k"] == 1 and cfg["swap"] == 1, cfg

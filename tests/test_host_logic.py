@@ -73,9 +73,29 @@ def test_data_parallel_and_mixed_plans_cover_the_problem(shape, col_major):
     check_cover(p, segs)
 
 
+@pytest.mark.parametrize("M", [8, 16, 32])
+def test_decode_shapes_up_to_32_rows_run_as_one_wave_of_whole_tiles(M):
+    # 224 tiles on 148 SMs: two CTAs per SM with half-size rings, one whole tile each.
+    p, segs = plan(M, 28672, 8192)
+    assert (p["swap"], p["stream_k"], p["cta_group"], p["stages"]) == (1, 0, 1, 5)
+    assert p["tiles"] == 224 and p["ctas"] == 224 and p["max_contrib"] == 0
+    check_cover(p, segs)
+    assert sorted(s[0] for s in segs) == list(range(224)) and all(s[3] == 128 for s in segs)
+    # not when the tiles fit one per SM, when there are more than two per SM, or for short K
+    assert plan(M, 148 * 128, 8192)[0]["ctas"] == 148
+    assert plan(M, 297 * 128, 8192)[0]["ctas"] == 148
+    assert plan(M, 28672, 512)[0]["ctas"] == 148
+    # forced on (also below one tile per SM) and off
+    assert plan(M, 100 * 128, 8192, tuning={7: 1})[0]["stages"] == 5
+    assert plan(64, 28672, 8192, tuning={7: 1})[0]["stages"] == 3
+    p, segs = plan(M, 28672, 8192, tuning={7: 0})
+    assert (p["stream_k"], p["ctas"]) == (1, 148)
+    check_cover(p, segs)
+
+
 @pytest.mark.parametrize("M", [16, 64, 128])
 def test_decode_shapes_use_swapped_stream_k(M):
-    p, segs = plan(M, 28672, 8192)
+    p, segs = plan(M, 28672, 8192, tuning={7: 0})
     assert (p["swap"], p["stream_k"], p["cta_group"]) == (1, 1, 1)
     assert p["block_n"] == M and p["Md"] == 28672 and p["tiles"] == 224 and p["ctas"] == 148
     check_cover(p, segs)
@@ -94,7 +114,7 @@ def test_decode_shapes_use_swapped_stream_k(M):
     assert set(per_worker.values()) <= {lo, lo + 1} and len(per_worker) == 148
     assert p["max_contrib"] == 2 + ppt
     # switched off, every CTA gets 193 or 194 of the 28672 (tile, k-block) units
-    p, segs = plan(M, 28672, 8192, tuning={4: 0})
+    p, segs = plan(M, 28672, 8192, tuning={4: 0, 7: 0})
     check_cover(p, segs)
     per_worker = defaultdict(int)
     for s in segs:
@@ -129,7 +149,7 @@ def test_plan_picks_tma_store_only_for_aligned_pitch():
 def test_workspace_counters_region_is_shape_independent():
     # Two different skinny shapes must agree on where the counters end and the partials begin;
     # the public size query needs a device, so the layout is checked through the plan instead.
-    a, _ = plan(16, 28672, 8192)
+    a, _ = plan(64, 28672, 8192)
     b, _ = plan(128, 3584, 8192)
     assert a["stream_k"] == b["stream_k"] == 1
 
