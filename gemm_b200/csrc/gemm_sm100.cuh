@@ -149,6 +149,10 @@ struct GemmConfig {
   static_assert(kCtaGroup == 1 || kTmemCols == 512,
                 "pair mode allocates all of tensor memory so both CTAs get column 0");
   static_assert(SMEM_TOTAL <= 232448, "exceeds 227 KB of shared memory per CTA");
+  // The last tile's store epilogue borrows one 4 KB box buffer per box from the idle ring.
+  static_assert(kEpiMode != kEpiTmaStore ||
+                    kEpiWarps * 4 * SMEM_EPI_WARP_BUF <= kStages * SMEM_STAGE,
+                "the ring must hold every box of a tile");
 };
 
 // One unit of work for a CTA (pair).
@@ -189,17 +193,22 @@ struct SegmentIter {
     phase = sk_tiles > 0 ? 0 : 3;
     splits = p.stream_k ? p.sk_splits : 0;
     worker_id = worker;
-    const long long nk = num_k_blocks > 0 ? num_k_blocks : 1;
-    u0 = total_units > 0 ? range_start(worker) : 0;
-    u1 = total_units > 0 ? range_start(worker + 1) : 0;
-    head_end = u0;
-    if (u0 % nk != 0) {
-      head_end = (u0 / nk + 1) * nk;
-      if (head_end > u1) head_end = u1;
+    u0 = u1 = head_end = tail_begin = whole = 0;
+    // Only launches with cut tiles pay for the 64-bit divisions below: they sit in front of
+    // every role's first action (the producer's first copy included).
+    if (total_units > 0 && splits == 0) {
+      const long long nk = num_k_blocks > 0 ? num_k_blocks : 1;
+      u0 = range_start(worker);
+      u1 = range_start(worker + 1);
+      head_end = u0;
+      if (u0 % nk != 0) {
+        head_end = (u0 / nk + 1) * nk;
+        if (head_end > u1) head_end = u1;
+      }
+      tail_begin = u1;
+      if (u1 % nk != 0 && (u1 / nk) * nk >= head_end) tail_begin = (u1 / nk) * nk;
+      whole = head_end;
     }
-    tail_begin = u1;
-    if (u1 % nk != 0 && (u1 / nk) * nk >= head_end) tail_begin = (u1 / nk) * nk;
-    whole = head_end;
   }
 
   __host__ __device__ __forceinline__ long long range_start(int c) const {
@@ -818,6 +827,18 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
     while (ok && it.next(seg, lane)) {
       const uint32_t acc = (Cfg::kNHalves == 1) ? (seg_idx & 1) : 0;
       const uint32_t acc_phase = (Cfg::kNHalves == 1) ? ((seg_idx >> 1) & 1) : (seg_idx & 1);
+      // Is this the CTA's last segment?  Then, once its accumulator is complete, nothing reads
+      // or fills the operand ring any more (every copy issued has been consumed by an MMA that
+      // has finished), and the store epilogue may use it as staging: every box of the tile gets
+      // a buffer of its own and the TMA stores go out back to back instead of waiting, box by
+      // box, for the one or two regular buffers to be read out (~1 us each) - that wait is
+      // otherwise the exposed tail of every launch.
+      bool ring_is_free = false;
+      if (Cfg::kEpiMode == kEpiTmaStore && p.dyn_pieces == 0) {
+        SegmentIter peek = it.it;
+        Segment unused;
+        ring_is_free = !peek.next(unused);
+      }
       // Everything that does not need the accumulator is worked out before the wait: with a
       // two-half tile the tensor pipe idles from the moment the barrier fires until this warp has
       // read its share, and the index arithmetic alone was ~1500 cycles of that.
@@ -834,9 +855,15 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
       int got_i = 0;
       // Two-half tiles sleep on the early notice (barrier slot 1, raised when the tile's last MMA
       // has been issued) and then poll the real barrier from inside the read-out loop below.
-      if (lane == 0)
-        got_i = mbar_wait(tmem_full_bar + 8 * (Cfg::kNHalves == 2 ? 1u : acc), acc_phase, abort_flag,
-                          static_cast<uint32_t>(p.epi_wait_hint_ns)) ? 1 : 0;
+      // The CTA's last accumulator is awaited with non-blocking tests: nothing hides a late
+      // wake-up from a suspended wait there (it can be microseconds), it is the launch's tail.
+      if (lane == 0) {
+        const uint32_t bar = tmem_full_bar + 8 * (Cfg::kNHalves == 2 ? 1u : acc);
+        got_i = (ring_is_free && Cfg::kNHalves == 1)
+            ? (mbar_wait<false, true>(bar, acc_phase, abort_flag) ? 1 : 0)
+            : (mbar_wait(bar, acc_phase, abort_flag,
+                         static_cast<uint32_t>(p.epi_wait_hint_ns)) ? 1 : 0);
+      }
       const bool got = __shfl_sync(0xffffffffu, got_i, 0) != 0;
       wait_timer.end();
       if (!got) {
@@ -1009,13 +1036,16 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
           }
         }
         released = true;
-        const uint32_t row_addr = buf + lane * 128u;
         const uint32_t sw = lane & 7u;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int h = i >> 1, b = i & 1;
           const int c = h * BLOCK_N + warp_set * (BLOCK_N / 2) + b * Cfg::EPI_COLS;
-          if (lane == 0) tma_store_wait_read<0>();   // the previous box has left the buffer
+          const bool own_buf = (i == 0) || !ring_is_free;
+          const uint32_t box_buf = own_buf
+              ? buf : ring + static_cast<uint32_t>((warp - 2) * 3 + (i - 1)) * Cfg::SMEM_EPI_WARP_BUF;
+          const uint32_t row_addr = box_buf + lane * 128u;
+          if (own_buf && lane == 0) tma_store_wait_read<0>();   // the previous box has left it
           __syncwarp();
 #pragma unroll
           for (int j = 0; j < 8; ++j)
@@ -1026,8 +1056,8 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
           __syncwarp();
           if (lane == 0) {
             if (my_row0 < p.Md && col0 + c < p.Nd) {
-              if (p.l2_hints & 4) tma_store_2d_hint(&tmap_d, buf, col0 + c, my_row0, pol_d);
-              else tma_store_2d(&tmap_d, buf, col0 + c, my_row0);
+              if (p.l2_hints & 4) tma_store_2d_hint(&tmap_d, box_buf, col0 + c, my_row0, pol_d);
+              else tma_store_2d(&tmap_d, box_buf, col0 + c, my_row0);
             }
             tma_store_commit();
           }
@@ -1045,7 +1075,9 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
               ? i * Cfg::EPI_COLS
               : (i >> 1) * BLOCK_N + warp_set * (BLOCK_N / 2) + (i & 1) * Cfg::EPI_COLS;
           const bool last_of_accumulator = (Cfg::kNHalves == 1) ? (i == kBoxes - 1) : ((i & 1) == 1);
-          const uint32_t buf = warp_stage + (store_count % Cfg::kEpiBufs) * Cfg::SMEM_EPI_WARP_BUF;
+          const uint32_t buf = ring_is_free
+              ? ring + static_cast<uint32_t>((warp - 2) * kBoxes + i) * Cfg::SMEM_EPI_WARP_BUF
+              : warp_stage + (store_count % Cfg::kEpiBufs) * Cfg::SMEM_EPI_WARP_BUF;
           uint32_t r0[32], r1[32];
           __syncwarp();
           tmem_ld_32x32b_x32(taddr + c, r0);
@@ -1064,7 +1096,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
             released = true;
           }
           // The store issued kEpiBufs boxes ago read from this buffer; make sure it is done.
-          if (lane == 0) tma_store_wait_read<Cfg::kEpiBufs - 1>();
+          if (!ring_is_free && lane == 0) tma_store_wait_read<Cfg::kEpiBufs - 1>();
           __syncwarp();
           if (tile_partials != nullptr) {
             const float* base = tile_partials + static_cast<size_t>(c) * Cfg::TILE_M +
