@@ -122,9 +122,11 @@ struct GemmConfig {
   // epilogue warps (four per half, so both halves drain at once), one buffer each.
   static constexpr int kEpiWarps = 4 * kNHalves;
   static constexpr int kEpiBufs = (kNHalves == 1) ? 2 : 1;
-  // Direct mode stages a warp's 32 rows x BLOCK_N columns transposed ([column][32 rows], 64 B per
-  // column) so that a transposed result leaves as 16-byte vectors instead of 2-byte scalars.
-  static constexpr int SMEM_EPI_T_WARP = BLOCK_N * 64;
+  // Direct mode works through the accumulator kDirectCols columns at a time and stages each such
+  // step of a warp's 32 rows transposed ([column][32 rows], 64 B per column) so that a transposed
+  // result leaves as 16-byte vectors instead of 2-byte scalars.
+  static constexpr int kDirectCols = (BLOCK_N >= 32) ? 32 : 16;
+  static constexpr int SMEM_EPI_T_WARP = kDirectCols * 64;
   static constexpr int SMEM_EPI = (kEpiMode == kEpiTmaStore) ? kEpiWarps * kEpiBufs * SMEM_EPI_WARP_BUF
                                                              : 4 * SMEM_EPI_T_WARP;
   static constexpr int SMEM_BARRIERS = (2 * kStages + 8) * 8 + 16;
@@ -1156,10 +1158,10 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
         transposed = (p.out_stride_r == 1) && ((p.out_stride_c & 7) == 0) &&
                      ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
         const uint32_t stg = epi_base + (warp - 2) * Cfg::SMEM_EPI_T_WARP;
-        if (transposed) __syncwarp();   // the previous tile's write-out has left the staging
         // 32 columns per step where the tile has them: half as many dependent round trips to
         // the partials of a cut tile as with 16.
-        constexpr int kDC = (BLOCK_N >= 32) ? 32 : 16;
+        constexpr int kDC = Cfg::kDirectCols;
+        const int n0 = row0 + static_cast<int>(quad) * 32 + static_cast<int>(lane & 3u) * 8;
 #pragma unroll 1
         for (int c = 0; c < BLOCK_N; c += kDC) {
           uint32_t r[kDC];
@@ -1178,10 +1180,35 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
           const int col = col0 + c;
           if (p.fuse) fused_epilogue<kDC>(r, p, row, col);
           if (transposed) {
+            // (the __syncwarp in front of this step's tcgen05.ld is also what keeps these writes
+            // behind the previous step's reads of the staging buffer)
 #pragma unroll
             for (int j = 0; j < kDC; ++j)
-              st_shared_b16(stg + static_cast<uint32_t>(c + j) * 64u + lane * 2u,
+              st_shared_b16(stg + static_cast<uint32_t>(j) * 64u + lane * 2u,
                             __bfloat16_as_ushort(__float2bfloat16_rn(__uint_as_float(r[j]))));
+            __syncwarp();
+            // Write-out of the staged step: column m of D is 32 contiguous bf16 (64 B) of the
+            // result; four lanes cover one column, the warp covers eight columns per store.
+#pragma unroll
+            for (int m = static_cast<int>(lane >> 2); m < kDC; m += 8) {
+              const int colm = col + m;
+              if (colm >= p.Nd || n0 >= p.Md) continue;
+              const long long off = static_cast<long long>(colm) * p.out_stride_c + n0;
+              uint32_t v[4];
+              ld_shared_v4(stg + static_cast<uint32_t>(m) * 64u + (lane & 3u) * 16u, v);
+              if (n0 + 8 <= p.Md) {
+                if (off + 8 > p.out_span) {
+                  report_error(p, abort_flag, kDevBounds, seg_idx, 3);
+                } else {
+                  *reinterpret_cast<uint4*>(p.out + off) = make_uint4(v[0], v[1], v[2], v[3]);
+                }
+              } else {
+                const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(v);
+                for (int j = 0; j < 8 && n0 + j < p.Md; ++j) {
+                  if (off + j < p.out_span) p.out[off + j] = e[j];
+                }
+              }
+            }
           } else
           if (row < p.Md && col < p.Nd) {
             const int last_col = min(col + kDC - 1, p.Nd - 1);
@@ -1223,34 +1250,6 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
         const uint32_t which = acc;
         if (kCtaGroup == 2) mbar_arrive_cluster(leader_tmem_empty + 8 * which);
         else mbar_arrive(tmem_empty_bar + 8 * which);
-      }
-      if constexpr (Cfg::kEpiMode == kEpiDirect) {
-        if (finish && transposed) {
-          // Write-out of the staged tile: column m of D is 32 contiguous bf16 (64 B) of the
-          // result; four lanes cover one column, the warp covers eight columns per store.
-          const uint32_t stg = epi_base + (warp - 2) * Cfg::SMEM_EPI_T_WARP;
-          const int n0 = row0 + static_cast<int>(quad) * 32 + static_cast<int>(lane & 3u) * 8;
-#pragma unroll 1
-          for (int m = static_cast<int>(lane >> 2); m < BLOCK_N; m += 8) {
-            const int col = col0 + m;
-            if (col >= p.Nd || n0 >= p.Md) continue;
-            const long long off = static_cast<long long>(col) * p.out_stride_c + n0;
-            uint32_t v[4];
-            ld_shared_v4(stg + static_cast<uint32_t>(m) * 64u + (lane & 3u) * 16u, v);
-            if (n0 + 8 <= p.Md) {
-              if (off + 8 > p.out_span) {
-                report_error(p, abort_flag, kDevBounds, seg_idx, 3);
-              } else {
-                *reinterpret_cast<uint4*>(p.out + off) = make_uint4(v[0], v[1], v[2], v[3]);
-              }
-            } else {
-              const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(v);
-              for (int j = 0; j < 8 && n0 + j < p.Md; ++j) {
-                if (off + j < p.out_span) p.out[off + j] = e[j];
-              }
-            }
-          }
-        }
       }
       ++seg_idx;
     }

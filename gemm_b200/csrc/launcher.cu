@@ -44,11 +44,11 @@ constexpr double kWideTileSpeed = 1650.0;
 // time the store epilogue of one tile takes (both measured with the phase timers).
 constexpr double kHandOverUs = 3.5;
 constexpr double kEpilogueUs = 3.0;
-// Widest tile (columns) that has a half-size-ring kernel for two CTAs per SM, and the widest for
-// which the launcher picks it on its own: at 64 columns only three ring stages fit and stream-K
-// over full-size rings is faster (M=64 decode: 83.6 us against 84.5 us).
+// Widest tile (columns) that has a half-size-ring kernel for two CTAs per SM (four ring stages of
+// 24 KB still fit at 64 columns; at 128 only three of 32 KB would), and the widest for which the
+// launcher picks it on its own.
 constexpr int kResidentMaxColumns = 64;
-constexpr int kResidentAutoColumns = 32;
+constexpr int kResidentAutoColumns = 64;
 // k-blocks per dynamically claimed piece of the stream-K tail pool.
 constexpr int kDynPieceKBlocks = 16;
 // Row chunks the host entry point cuts the uploaded operand into (one product launch each).
@@ -90,7 +90,7 @@ const KernelEntry* kernel_table(int* count) {
       make_entry<GemmConfig<1, 16, 12, kEpiDirect>>(),
       // Half-size rings: two CTAs per SM, one whole tile each (skinny shapes with between one and
       // two tiles per SM, which then need no cut tiles and no closing reduction).
-      make_entry<GemmConfig<1, 64, 3, kEpiDirect>>(),
+      make_entry<GemmConfig<1, 64, 4, kEpiDirect>>(),
       make_entry<GemmConfig<1, 32, 5, kEpiDirect>>(),
       make_entry<GemmConfig<1, 16, 5, kEpiDirect>>(),
   };
@@ -394,7 +394,8 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
   // on 148 SMs) run as ONE wave of whole tiles, two CTAs per SM with half-size rings: every CTA
   // streams one tile's rows over all of K, nothing is cut, nothing has to be summed at the end.
   // cuBLAS' choice for M=16 has the same shape (112 whole tiles of 256 rows, no split-K).
-  // Measured (CUDA-graph replays, M x 28672 x 8192): M=16 78.7 -> 74.7 us, M=32 83.4 -> 77.6 us.
+  // Measured (CUDA-graph replays, M x 28672 x 8192): M=16 78.3 -> 74.2 us, M=32 81.8 -> 76.9 us,
+  // M=64 84.4 -> 83.0 us (K=4096: 48.2 -> 40.2 us).
   // Tuning key 7: -1 auto, 0 never, 1 whenever the kernel exists and the tiles fit.
   int per_sm = 1;
   if (epi == kEpiDirect && cta_group == 1 && ov.tuning[7] != 0 && ov.stream_k <= 0 &&
