@@ -76,7 +76,8 @@ KernelEntry make_entry() {
 }
 
 // Stage counts fill the 227 KB of shared memory; a CTA that owns more than half of it is alone on
-// its SM, which is what makes its tensor-memory allocation safe from starvation.
+// its SM, which is what makes its tensor-memory allocation safe from starvation.  The last three
+// entries are built to share an SM two at a time and hold at most 128 columns each.
 const KernelEntry* kernel_table(int* count) {
   static const KernelEntry table[] = {
       make_entry<GemmConfig<1, 256, 4, kEpiTmaStore>>(),
@@ -328,7 +329,7 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
   if (epi == kEpiDirect && block_n > 128) block_n = 128;
   if (cta_group == 2 && (epi != kEpiTmaStore || block_n < 128)) cta_group = 1;
   if (epi == kEpiTmaStore) {
-    // Choose among the four TMA-store kernels by estimated time: waves of tiles over the
+    // Choose among the TMA-store kernels by estimated time: waves of tiles over the
     // workers (SMs, or SM pairs) times the work of one tile per SM, divided by the throughput
     // each kernel reached at 8192^3 on a B200 (TFLOP/s, measured).  Overrides pin a field.
     struct Candidate { int cta_group, block_n, halves; double speed; };
