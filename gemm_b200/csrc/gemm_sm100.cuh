@@ -58,6 +58,11 @@ struct GemmParams {
   int epi_wait_hint_ns;      // suspend hint of the epilogue's wait for an accumulator (0 = none)
   int main_wait_hint_ns;     // suspend hint of the producer's and the MMA warp's ring waits
   int wide_prologue;         // two-half tiles: k-blocks issued for half 0 alone at a tile's start
+  // Wave pacing (plain round-robin schedules of many waves): an arrival counter in global
+  // memory, zero between launches, and how long a worker may wait at a wave's start for the
+  // others to arrive.  Null = off.
+  int* pace_counter;
+  int pace_timeout_ns;
   // Direct epilogue / split partials.
   __nv_bfloat16* out;
   long long out_stride_r, out_stride_c;
@@ -316,9 +321,9 @@ struct SegmentIter {
   }
 };
 
-// Grouped raster: consecutive tile ids walk down `group_m` tile rows before moving one tile
-// column to the right, so the tiles in flight at any moment share a few row panels of X and a
-// few column panels of Y in L2.  (The reference rasters row-major, neogemmV02.cu:190-191.)
+// Grouped, serpentine raster: consecutive tile ids walk down `group_m` tile rows before moving one
+// tile column on, so the tiles in flight at any moment share a few row panels of X and a few
+// column panels of Y in L2; the direction across the columns alternates from group to group.  (The reference rasters row-major, neogemmV02.cu:190-191.)
 __host__ __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& tm, int& tn) {
   const int group_size = p.group_m * p.num_n_tiles;
   const int group = tile / group_size;
@@ -328,6 +333,9 @@ __host__ __device__ __forceinline__ void tile_coords(const GemmParams& p, int ti
   const int local = tile - group * group_size;
   tm = first_m + local % rows;
   tn = local / rows;
+  // Odd groups walk the tile columns backwards: the column panels of Y that the previous group
+  // touched last are the first ones the next group asks for, while they are still in L2.
+  if (group & 1) tn = p.num_n_tiles - 1 - tn;
 }
 
 // Phase timers, the counterpart of the per-CTA load/compute/store cycle records the reference's
@@ -364,6 +372,40 @@ __device__ __forceinline__ void report_error(const GemmParams& p, volatile int* 
     p.status[3] = aux;
     __threadfence_system();
   }
+}
+
+// Wave pacing.  SM clocks differ by a few per cent between GPCs, so with a static round-robin
+// schedule the workers drift apart over a long launch (55 waves at 65536 x 8192 x 8192: the
+// fastest are whole tiles ahead by the end).  Tiles of one wave share their operand panels through
+// L2 only while they walk K roughly together; once the drift exceeds what L2 holds, every worker
+// fetches its panels from DRAM on its own (measured there: 9.7 GB read against 6.2 GB by cuBLAS and
+// 6.9 GB for workers in step), and on a power-capped GPU the extra traffic costs clock.
+// So the producer of every worker (the leader CTA of a pair) reports its arrival at the start of
+// each wave after the first and waits until all workers with a tile in that wave have arrived.
+// The launch ends with its slowest worker either way; the fast ones idle between waves instead of
+// at the end.  The wait is soft: it gives up after pace_timeout_ns and nothing depends on it.
+// The counter returns to zero with the launch's last arrival.
+__device__ __forceinline__ void pace_wave(const GemmParams& p, int wave, int num_workers,
+                                          uint32_t lane) {
+  if (lane == 0) {
+    const int total = p.num_tiles - num_workers;                    // arrivals of the whole launch
+    const int in_wave = min(num_workers, p.num_tiles - wave * num_workers);
+    const int need = (wave - 1) * num_workers + in_wave;            // all of this wave have arrived
+    const int mine = atomicAdd(p.pace_counter, 1) + 1;
+    if (mine == total) {
+      *reinterpret_cast<volatile int*>(p.pace_counter) = 0;          // nobody arrives after this
+    } else if (mine < need) {
+      const uint64_t t0 = ptx::globaltimer_ns();
+      for (;;) {
+        const int seen = *reinterpret_cast<volatile int*>(p.pace_counter);
+        // seen < mine: the counter was reset, i.e. the launch's last arrival has happened
+        if (seen >= need || seen < mine) break;
+        if (ptx::globaltimer_ns() - t0 > static_cast<uint64_t>(p.pace_timeout_ns)) break;
+        __nanosleep(100);
+      }
+    }
+  }
+  __syncwarp();
 }
 
 // Where a role gets its segments from: first the static sequence every role derives on its own
@@ -593,6 +635,8 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
       PhaseTimer wait_timer(timer_params), loop_timer(timer_params);
       loop_timer.begin();
       while (ok && it.next(seg, lane)) {
+        if (p.pace_counter != nullptr && is_leader && seg_idx >= 1)
+          pace_wave(p, seg_idx, num_workers, lane);
         int tm, tn;
         tile_coords(p, seg.tile, tm, tn);
         const int row_x = tm * Cfg::TILE_M + static_cast<int>(cta_rank) * Cfg::BLOCK_M;

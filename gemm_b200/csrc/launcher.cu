@@ -44,6 +44,12 @@ constexpr double kWideTileSpeed = 1650.0;
 // time the store epilogue of one tile takes (both measured with the phase timers).
 constexpr double kHandOverUs = 3.5;
 constexpr double kEpilogueUs = 3.0;
+// Wave pacing: launches of at least this many waves of whole tiles keep their workers in step
+// (see pace_wave in the kernel); each launch takes the next of kPaceSlots counters so that
+// launches in flight on different streams do not share one; a worker waits at most this long.
+constexpr int kPaceMinWaves = 8;
+constexpr int kPaceSlots = 32;
+constexpr int kPaceTimeoutNs = 20000;
 // Widest tile (columns) that has a half-size-ring kernel for two CTAs per SM (four ring stages of
 // 24 KB still fit at 64 columns; at 128 only three of 32 KB would), and the widest for which the
 // launcher picks it on its own.
@@ -121,6 +127,8 @@ struct DeviceState {
   int init_error = NEOGEMM_OK;
   int sm_count = 0;
   int* status_host = nullptr;  // mapped pinned memory: the kernel writes, the host reads
+  int* pace_counters = nullptr;   // kPaceSlots arrival counters, one 128-byte line each, zeroed
+  unsigned pace_next = 0;
   int* status_dev = nullptr;
   void* workspace = nullptr;   // library-owned stream-K scratch
   size_t workspace_bytes = 0;
@@ -139,7 +147,7 @@ bool g_encode_looked_up = false;
 
 struct Override {
   int cta_group = -1, block_n = -1, swap = -1, stream_k = -1, group_m = -1, max_ctas = -1;
-  int tuning[8] = {-1, -1, -1, -1, -1, -1, -1, -1};   // see neogemm_set_tuning
+  int tuning[9] = {-1, -1, -1, -1, -1, -1, -1, -1, -1};   // see neogemm_set_tuning
 };
 thread_local Override t_override;
 thread_local int t_last_config[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -195,6 +203,12 @@ DeviceState* device_state(int* code) {
     return nullptr;
   }
   std::memset(st.status_host, 0, 64);
+  // Arrival counters of the wave pacing; without them the kernels simply do not pace.
+  if (cudaMalloc(reinterpret_cast<void**>(&st.pace_counters), kPaceSlots * 128) != cudaSuccess ||
+      cudaMemset(st.pace_counters, 0, kPaceSlots * 128) != cudaSuccess) {
+    cudaGetLastError();
+    st.pace_counters = nullptr;
+  }
   *code = NEOGEMM_OK;
   return &st;
 }
@@ -672,6 +686,18 @@ int gemm_device(const void* A, const void* B, void* C, int64_t M, int64_t N, int
   params.dyn_static_kb = plan.dyn_static_kb;
   params.max_contrib = plan.max_contrib;
   params.status = st->status_dev;
+  // Tuning key 8: wave pacing -1 auto (many waves of whole tiles), 0 off, 1 whenever applicable.
+  {
+    const int workers = plan.num_ctas / plan.cta_group;
+    const int want = t_override.tuning[8];
+    const bool applicable = !plan.stream_k && plan.epi == kEpiTmaStore &&
+                            st->pace_counters != nullptr && plan.num_tiles > workers;
+    if (applicable && want != 0 && (want == 1 || plan.num_tiles >= kPaceMinWaves * workers)) {
+      std::lock_guard<std::mutex> lock(g_mu);
+      params.pace_counter = st->pace_counters + (st->pace_next++ % kPaceSlots) * 32;
+      params.pace_timeout_ns = kPaceTimeoutNs;
+    }
+  }
   if (fusion.on) {
     params.fuse = 1;
     params.alpha = fusion.alpha;
@@ -915,7 +941,12 @@ int neogemm_clear_device_status(void) {
     return NEOGEMM_ERR_CUDA;
   }
   std::memset(st->status_host, 0, 64);
-  // A launch that gave up may have left stream-K arrival counters non-zero.
+  // A launch that gave up may have left wave-pacing or stream-K arrival counters non-zero.
+  if (st->pace_counters != nullptr &&
+      cudaMemset(st->pace_counters, 0, kPaceSlots * 128) != cudaSuccess) {
+    cudaGetLastError();
+    return NEOGEMM_ERR_CUDA;
+  }
   if (st->workspace != nullptr &&
       cudaMemset(st->workspace, 0, st->workspace_bytes) != cudaSuccess) {
     cudaGetLastError();
@@ -968,7 +999,7 @@ int neogemm_set_phase_timers(void* device_buffer, size_t bytes) {
 }
 
 int neogemm_set_tuning(int key, int value) {
-  if (key < 0 || key > 7 || (key == 6 && (value == 0 || value > 3)) || (key == 7 && value > 1) || (key == 5 && value > 3) || value > 1000000 || (key == 0 && value > 31) || (key == 3 && value > 1) ||
+  if (key < 0 || key > 8 || (key == 6 && (value == 0 || value > 3)) || (key >= 7 && value > 1) || (key == 5 && value > 3) || value > 1000000 || (key == 0 && value > 31) || (key == 3 && value > 1) ||
       (key == 4 && value > 4))
     return NEOGEMM_ERR_BAD_ARG;
   t_override.tuning[key] = value;

@@ -173,6 +173,9 @@ int neogemm_set_override(int cta_group, int block_n, int swap, int stream_k, int
  *   key 7: skinny shapes with between one and two tiles per SM as ONE wave of whole tiles, two
  *          CTAs per SM with half-size rings (no cut tiles, no closing sums): -1 chosen by the
  *          launcher, 0 never, 1 whenever such a kernel exists and all tiles fit at once.
+ *   key 8: wave pacing of launches with many waves of whole tiles (workers wait, briefly and
+ *          without obligation, for each other at the start of every wave so that tiles sharing
+ *          operand panels keep sharing them in L2): -1 from 8 waves on, 0 off, 1 from 2 waves on.
  * No counterpart in the reference (its maps only set L2 promotion, nemgemmV03.cu:52). */
 int neogemm_set_tuning(int key, int value);
 

@@ -111,3 +111,37 @@ def test_wide_pair_tile_is_deterministic_and_never_wide_when_switched_off():
     assert ops.device_status()[0] == 0
     # same k order per element in both kernels -> identical bits
     assert torch.equal(first.view(torch.int16), other.view(torch.int16))
+
+
+@pytest.mark.parametrize("shape", [(4096, 8192, 256), (8192, 8192, 1024), (5000, 3000, 640),
+                                   (16384, 4096, 512)])
+def test_wave_pacing_changes_neither_bits_nor_much_time(shape):
+    # Workers wait for each other at the start of every wave (an arrival counter in global
+    # memory that must be back at zero after every launch).  Forced on, also for short waves:
+    # same bits as without it, launch after launch, and no launch that sits out its time-outs.
+    from gemm_b200.inputs import make_problem
+    A, B = make_problem(*shape, seed=21)
+    dA, dB = A.cuda(), B.cuda()
+
+    def timed(n):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            out = ops.matmul(dA, dB)
+        e1.record()
+        e1.synchronize()
+        return out, e0.elapsed_time(e1) / n
+
+    ops.set_tuning("wave_pacing", 0)
+    try:
+        plain, _ = timed(3)
+        plain, t_plain = timed(10)
+        ops.set_tuning("wave_pacing", 1)
+        paced, _ = timed(3)
+        paced, t_paced = timed(10)
+    finally:
+        ops.set_tuning("wave_pacing", -1)
+    assert torch.equal(plain.view(torch.int16), paced.view(torch.int16))
+    assert ops.device_status()[0] == 0
+    assert t_paced <= 1.5 * t_plain + 0.05, (t_plain, t_paced)
+    run_case(*shape, tuning={"wave_pacing": 1})
