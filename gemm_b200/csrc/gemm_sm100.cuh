@@ -63,6 +63,9 @@ struct GemmParams {
   // others to arrive.  Null = off.
   int* pace_counter;
   int pace_timeout_ns;
+  // Whole tiles of odd waves walk K backwards: the k-slices of the row panel a worker group used
+  // last in one wave are the first ones the next wave asks for, while L2 still holds them.
+  int k_alternate;
   // Direct epilogue / split partials.
   __nv_bfloat16* out;
   long long out_stride_r, out_stride_c;
@@ -642,6 +645,10 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
         const int row_x = tm * Cfg::TILE_M + static_cast<int>(cta_rank) * Cfg::BLOCK_M;
         const int row_y = tn * Cfg::TILE_N + static_cast<int>(cta_rank) * Cfg::LOAD_N;
         const int kb_end = seg.kb_begin + seg.kb_count;
+        // Only the producer knows the direction: the MMA warp consumes ring slots in order and
+        // the sum of a tile's k-blocks does not care which came first (the order is fixed per
+        // tile, so results stay reproducible).
+        const bool reverse_k = p.k_alternate != 0 && (seg_idx & 1) != 0 && seg.n_contrib == 1;
         for (int kb = seg.kb_begin; kb < kb_end; ++kb) {
           wait_timer.begin();
           const bool got = __all_sync(0xffffffffu,
@@ -657,7 +664,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
           const uint32_t sx = ring + stage * Cfg::SMEM_STAGE;
           const uint32_t sy = sx + Cfg::SMEM_X;
           if (elect_one()) {
-            const int c0 = kb * Cfg::BLOCK_K;
+            const int c0 = (reverse_k ? (seg.kb_begin + kb_end - 1 - kb) : kb) * Cfg::BLOCK_K;
             if (kCtaGroup == 1) {
               mbar_arrive_expect_tx(full_bar + 8 * stage, Cfg::SMEM_STAGE);
               if (hint_x) tma_load_2d_hint(sx, &tmap_x, full_bar + 8 * stage, c0, row_x, pol_x);

@@ -47,6 +47,7 @@ constexpr double kEpilogueUs = 3.0;
 // Wave pacing: launches of at least this many waves of whole tiles keep their workers in step
 // (see pace_wave in the kernel); each launch takes the next of kPaceSlots counters so that
 // launches in flight on different streams do not share one; a worker waits at most this long.
+constexpr bool kDefaultKAlternate = false;
 constexpr int kPaceMinWaves = 8;
 constexpr int kPaceSlots = 32;
 constexpr int kPaceTimeoutNs = 20000;
@@ -147,7 +148,7 @@ bool g_encode_looked_up = false;
 
 struct Override {
   int cta_group = -1, block_n = -1, swap = -1, stream_k = -1, group_m = -1, max_ctas = -1;
-  int tuning[9] = {-1, -1, -1, -1, -1, -1, -1, -1, -1};   // see neogemm_set_tuning
+  int tuning[10] = {-1, -1, -1, -1, -1, -1, -1, -1, -1, -1};   // see neogemm_set_tuning
 };
 thread_local Override t_override;
 thread_local int t_last_config[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -698,6 +699,14 @@ int gemm_device(const void* A, const void* B, void* C, int64_t M, int64_t N, int
       params.pace_timeout_ns = kPaceTimeoutNs;
     }
   }
+  // Tuning key 9: alternate the K direction from wave to wave (-1 auto: plain round-robin
+  // schedules of TMA-store kernels with more than one wave; 0 off; 1 on for every schedule).
+  {
+    const int want = t_override.tuning[9];
+    const int workers = plan.num_ctas / plan.cta_group;
+    params.k_alternate = (want == 1 || (want < 0 && kDefaultKAlternate && !plan.stream_k &&
+                                        plan.epi == kEpiTmaStore && plan.num_tiles > workers)) ? 1 : 0;
+  }
   if (fusion.on) {
     params.fuse = 1;
     params.alpha = fusion.alpha;
@@ -999,7 +1008,7 @@ int neogemm_set_phase_timers(void* device_buffer, size_t bytes) {
 }
 
 int neogemm_set_tuning(int key, int value) {
-  if (key < 0 || key > 8 || (key == 6 && (value == 0 || value > 3)) || (key >= 7 && value > 1) || (key == 5 && value > 3) || value > 1000000 || (key == 0 && value > 31) || (key == 3 && value > 1) ||
+  if (key < 0 || key > 9 || (key == 6 && (value == 0 || value > 3)) || (key >= 7 && value > 1) || (key == 5 && value > 3) || value > 1000000 || (key == 0 && value > 31) || (key == 3 && value > 1) ||
       (key == 4 && value > 4))
     return NEOGEMM_ERR_BAD_ARG;
   t_override.tuning[key] = value;

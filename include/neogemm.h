@@ -176,6 +176,10 @@ int neogemm_set_override(int cta_group, int block_n, int swap, int stream_k, int
  *   key 8: wave pacing of launches with many waves of whole tiles (workers wait, briefly and
  *          without obligation, for each other at the start of every wave so that tiles sharing
  *          operand panels keep sharing them in L2): -1 from 8 waves on, 0 off, 1 from 2 waves on.
+ *   key 9: whole tiles of odd waves walk K backwards, so that the k-slices of a row panel used
+ *          last by one wave are asked for first by the next (fewer DRAM reads: 838 -> 752 MB at
+ *          8192^3; no measurable gain in time, and the sums of those tiles then round like a
+ *          reversed k loop): 1 on, 0 or -1 off.
  * No counterpart in the reference (its maps only set L2 promotion, nemgemmV03.cu:52). */
 int neogemm_set_tuning(int key, int value);
 

@@ -145,3 +145,24 @@ def test_wave_pacing_changes_neither_bits_nor_much_time(shape):
     assert ops.device_status()[0] == 0
     assert t_paced <= 1.5 * t_plain + 0.05, (t_plain, t_paced)
     run_case(*shape, tuning={"wave_pacing": 1})
+
+
+@pytest.mark.parametrize("shape", [(4096, 8192, 256), (8192, 4096, 1096), (5000, 3000, 640),
+                                   (2048, 2048, 8192)])
+def test_alternating_k_direction(shape):
+    # Odd waves fetch their k-blocks last to first (ragged last k-block included); the MMA warp
+    # does not know.  Parity with the oracle and the same bits launch after launch.
+    from gemm_b200.inputs import make_problem
+    stats, cfg = run_case(*shape, tuning={"k_direction_alternates": 1})
+    run_case(*shape, tuning={"k_direction_alternates": 1}, col_major=True)
+    A, B = make_problem(*shape, seed=33)
+    dA, dB = A.cuda(), B.cuda()
+    ops.set_tuning("k_direction_alternates", 1)
+    try:
+        first = ops.matmul(dA, dB).clone()
+        for _ in range(4):
+            assert torch.equal(first.view(torch.int16), ops.matmul(dA, dB).view(torch.int16))
+    finally:
+        ops.set_tuning("k_direction_alternates", -1)
+    torch.cuda.synchronize()
+    assert ops.device_status()[0] == 0
