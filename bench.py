@@ -48,7 +48,7 @@ WORKLOADS = {
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch of the dominant kernel,
 # from the ncu captures summarised under profiles/ (same bench.py command lines).
 NCU_TRAFFIC_BYTES = {
-    "8192": 936725248 + 139557376,
+    "8192": 835020800 + 140674560,
     "decode16": 470125312 + 3457792,
     "decode128": 473134848 + 11559424,
 }
