@@ -320,3 +320,10 @@ def test_bounded_wait_expires_into_an_error_code_and_the_library_recovers():
     ops.clear_device_status()
     assert ops.device_status() == (0, 0, 0, 0)
     run_case(128, 128, 64)              # same context, same library: works again
+
+
+@pytest.mark.parametrize("shape", [(512, 512, 8192), (256, 256, 4096), (300, 520, 4104)])
+def test_handful_of_tiles_under_long_k(shape):
+    stats, cfg = run_case(*shape)
+    assert (cfg["block_n"], cfg["stream_k"]) == (64, 1), cfg
+    run_case(*shape, col_major=True)

@@ -222,3 +222,14 @@ def test_last_partial_wave_of_large_shapes_is_cut():
 def test_hybrid_schedules_cover_the_problem(shape, override):
     p, segs = plan(*shape, override=override)
     check_cover(p, segs)
+
+
+def test_handful_of_tiles_under_long_k_is_cut_into_k_chunks():
+    # 512 x 512 x 8192: 64-column direct-store tiles, every tile cut, one chunk per CTA.
+    p, segs = plan(512, 512, 8192)
+    assert (p["epi"], p["block_n"], p["stream_k"], p["cta_group"]) == (1, 64, 1, 1)
+    assert p["tiles"] == 32 and p["ctas"] == 128
+    check_cover(p, segs)
+    # not with short K, nor with more 128 x 128 tiles than an eighth of the SMs
+    assert plan(512, 512, 2048)[0]["epi"] == 0
+    assert plan(1024, 1024, 8192)[0]["epi"] == 0
