@@ -50,7 +50,7 @@ WORKLOADS = {
 NCU_TRAFFIC_BYTES = {
     "8192": 835020800 + 140674560,
     "decode16": 470125312 + 3457792,
-    "decode128": 473134848 + 11559424,
+    "decode128": 472712704 + 3770624,
 }
 
 

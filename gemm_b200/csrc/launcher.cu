@@ -51,11 +51,11 @@ constexpr bool kDefaultKAlternate = false;
 constexpr int kPaceMinWaves = 8;
 constexpr int kPaceSlots = 32;
 constexpr int kPaceTimeoutNs = 20000;
-// Widest tile (columns) that has a half-size-ring kernel for two CTAs per SM (four ring stages of
-// 24 KB still fit at 64 columns; at 128 only three of 32 KB would), and the widest for which the
+// Widest tile (columns) that has a half-size-ring kernel for two CTAs per SM (five ring stages
+// up to 32 columns, four of 24 KB at 64, three of 32 KB at 128), and the widest for which the
 // launcher picks it on its own.
-constexpr int kResidentMaxColumns = 64;
-constexpr int kResidentAutoColumns = 64;
+constexpr int kResidentMaxColumns = 128;
+constexpr int kResidentAutoColumns = 128;
 // k-blocks per dynamically claimed piece of the stream-K tail pool.
 constexpr int kDynPieceKBlocks = 16;
 // Row chunks the host entry point cuts the uploaded operand into (one product launch each).
@@ -98,6 +98,7 @@ const KernelEntry* kernel_table(int* count) {
       make_entry<GemmConfig<1, 16, 12, kEpiDirect>>(),
       // Half-size rings: two CTAs per SM, one whole tile each (skinny shapes with between one and
       // two tiles per SM, which then need no cut tiles and no closing reduction).
+      make_entry<GemmConfig<1, 128, 3, kEpiDirect>>(),
       make_entry<GemmConfig<1, 64, 4, kEpiDirect>>(),
       make_entry<GemmConfig<1, 32, 5, kEpiDirect>>(),
       make_entry<GemmConfig<1, 16, 5, kEpiDirect>>(),
@@ -422,7 +423,7 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
   // streams one tile's rows over all of K, nothing is cut, nothing has to be summed at the end.
   // cuBLAS' choice for M=16 has the same shape (112 whole tiles of 256 rows, no split-K).
   // Measured (CUDA-graph replays, M x 28672 x 8192): M=16 78.3 -> 74.2 us, M=32 81.8 -> 76.9 us,
-  // M=64 84.4 -> 83.0 us (K=4096: 48.2 -> 40.2 us).
+  // M=64 84.4 -> 83.0 us (K=4096: 48.2 -> 40.2 us), M=128 87.8 -> 82.8 us, M=96 91.6 -> 84.3 us.
   // Tuning key 7: -1 auto, 0 never, 1 whenever the kernel exists and the tiles fit.
   int per_sm = 1;
   if (epi == kEpiDirect && cta_group == 1 && ov.tuning[7] != 0 && ov.stream_k <= 0 &&

@@ -34,22 +34,24 @@ def test_config_8192_cube():
 def test_config_decode_shapes(M):
     stats, cfg = run_case(M, 28672, 8192)
     assert cfg["swap"] == 1, cfg
-    if M <= 64:   # one wave of 224 whole tiles, two CTAs to an SM
-        assert (cfg["stream_k"], cfg["ctas"], cfg["stages"]) == (0, 224, 5 if M <= 32 else 4), cfg
-    else:         # stream-K over 148 CTAs
-        assert (cfg["stream_k"], cfg["ctas"]) == (1, 148), cfg
+    # one wave of 224 whole tiles, two CTAs to an SM
+    stages = 5 if M <= 32 else (4 if M <= 64 else 3)
+    assert (cfg["stream_k"], cfg["ctas"], cfg["stages"]) == (0, 224, stages), cfg
+    stats, cfg = run_case(M, 28672, 8192, tuning={"two_ctas_per_sm": 0})   # stream-K over 148 CTAs
+    assert (cfg["stream_k"], cfg["ctas"]) == (1, 148), cfg
     run_case(M, 28672, 8192, col_major=True)
 
 
 @pytest.mark.parametrize("shape", [(16, 28672, 8192), (8, 19000, 1024), (24, 30000, 2048),
-                                   (64, 28672, 4096), (40, 20008, 1536), (1, 37000, 1024)])
+                                   (64, 28672, 4096), (40, 20008, 1536), (1, 37000, 1024),
+                                   (100, 20000, 2048), (128, 28672, 1024)])
 def test_two_ctas_per_sm_whole_tiles(shape):
     # Half-size rings, every tile resident at once (forced, so that the 64-column kernel and
     # shapes the launcher would not pick on its own run too); ragged rows and K, both layouts,
     # and the stream-K plan of the same shape must give the same bits where no tile is cut
     # differently - checked against the oracle, and launch to launch for determinism.
     stats, cfg = run_case(*shape, tuning={"two_ctas_per_sm": 1})
-    assert cfg["stream_k"] == 0 and cfg["ctas"] == cfg["tiles"] and cfg["stages"] in (4, 5), cfg
+    assert cfg["stream_k"] == 0 and cfg["ctas"] == cfg["tiles"] and cfg["stages"] in (3, 4, 5), cfg
     run_case(*shape, tuning={"two_ctas_per_sm": 1}, col_major=True)
     A, B = make_problem(*shape, seed=5)
     dA, dB = A.cuda(), B.cuda()
