@@ -44,6 +44,14 @@ def _load() -> ctypes.CDLL:
     lib.neogemm_bf16_nt_noalloc.restype = c_int
     lib.neogemm_bf16_nt_noalloc.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                             c_int64, c_int64, c_int64, c_int64, c_int, c_void_p]
+    lib.neogemm_noalloc_init.restype = c_int
+    lib.neogemm_noalloc_init.argtypes = []
+    lib.neogemm_noalloc_status.restype = c_int
+    lib.neogemm_noalloc_status.argtypes = [POINTER(c_int), c_void_p]
+    lib.neogemm_noalloc_clear_status.restype = c_int
+    lib.neogemm_noalloc_clear_status.argtypes = []
+    lib.neogemm_debug_wait_expiry_noalloc.restype = c_int
+    lib.neogemm_debug_wait_expiry_noalloc.argtypes = [ctypes.c_uint]
     lib.neogemm_workspace_bytes.restype = c_size_t
     lib.neogemm_workspace_bytes.argtypes = [c_int64, c_int64, c_int64, c_int]
     lib.neogemm_bf16_nt_host.restype = c_int

@@ -47,6 +47,9 @@ constexpr double kEpilogueUs = 3.0;
 // Wave pacing: launches of at least this many waves of whole tiles keep their workers in step
 // (see pace_wave in the kernel); each launch takes the next of kPaceSlots counters so that
 // launches in flight on different streams do not share one; a worker waits at most this long.
+// More than kPaceSlots paced launches in flight at once wrap around and share counters: results
+// are unaffected (the wait is soft, nothing depends on it) but a worker that reads a foreign count
+// may idle up to the time-out at a wave's start.
 constexpr bool kDefaultKAlternate = false;
 constexpr int kPaceMinWaves = 8;
 constexpr int kPaceSlots = 32;
@@ -132,8 +135,10 @@ struct DeviceState {
   int* pace_counters = nullptr;   // kPaceSlots arrival counters, one 128-byte line each, zeroed
   unsigned pace_next = 0;
   int* status_dev = nullptr;
-  void* workspace = nullptr;   // library-owned stream-K scratch
+  void* workspace = nullptr;   // library-owned stream-K scratch (grow-only)
   size_t workspace_bytes = 0;
+  std::vector<void*> retired_workspaces;   // outgrown scratch buffers, kept for work in flight
+  std::mutex host_entry_mu;    // one neogemm_bf16_nt_host call at a time per device
   void* stage[3] = {nullptr, nullptr, nullptr};  // device copies of A, B, C for the host entry
   size_t stage_bytes[3] = {0, 0, 0};
   bool attr_done[16] = {};
@@ -320,7 +325,7 @@ int hybrid_splits(int rest, int workers, int num_k_blocks, int min_chunk = 8) {
 // pm x pn is the matrix as stored (row-major, pitch ldc): [M,N] for row-major C, [N,M] for the
 // reference's column-major C.
 int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int sm_count,
-              const Override& ov, Plan* plan, bool allow_hybrid = true) {
+              const Override& ov, Plan* plan, bool allow_hybrid = true, bool allow_dyn_pool = true) {
   Plan p;
   const bool tma_store_ok = (ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
 
@@ -506,7 +511,7 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
       // at M=16); from 32 columns on the extra partial round trips cost more than the balancing
       // gains (M=32: 78.8 us without, 83.2 us with).
       const int want = ov.tuning[4] >= 0 ? ov.tuning[4] : (block_n <= 16 ? kDefaultDynPieces : 0);
-      if (want > 0 && p.num_k_blocks >= 64 && cta_group == 1 && allow_hybrid) {
+      if (want > 0 && p.num_k_blocks >= 64 && cta_group == 1 && allow_dyn_pool) {
         p.dyn_ppt = std::min(want, 4);
         p.dyn_piece_kb = kDynPieceKBlocks;
         p.dyn_static_kb = p.num_k_blocks - p.dyn_ppt * kDynPieceKBlocks;
@@ -549,18 +554,32 @@ int validate(const void* A, const void* B, const void* C, int64_t M, int64_t N, 
   return NEOGEMM_OK;
 }
 
-int ensure_workspace(DeviceState* st, size_t bytes) {
+// Library-owned stream-K scratch.  It only ever grows, and a buffer it has outgrown stays
+// allocated: launches still queued, and CUDA graphs captured earlier with workspace == NULL,
+// keep pointing at the old one (sizes at least double, so the retired buffers add up to less than
+// the live one).  Growing means cudaMalloc + cudaMemset, which a capturing stream does not allow:
+// then the call is refused and the caller makes one plain call first, or passes its own workspace.
+int ensure_workspace(DeviceState* st, size_t bytes, cudaStream_t stream) {
   if (bytes <= st->workspace_bytes) return NEOGEMM_OK;
-  if (st->workspace != nullptr) cudaFree(st->workspace);
-  st->workspace = nullptr;
-  st->workspace_bytes = 0;
-  const size_t want = std::max(bytes, static_cast<size_t>(64) << 20);
-  if (cudaMalloc(&st->workspace, want) != cudaSuccess ||
-      cudaMemset(st->workspace, 0, want) != cudaSuccess) {
+  cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &capturing) != cudaSuccess) {
     cudaGetLastError();
-    st->workspace = nullptr;
+    return NEOGEMM_ERR_CUDA;
+  }
+  if (capturing != cudaStreamCaptureStatusNone) return NEOGEMM_ERR_WORKSPACE;
+  const size_t want = std::max({bytes, 2 * st->workspace_bytes, static_cast<size_t>(64) << 20});
+  void* fresh = nullptr;
+  if (cudaMalloc(&fresh, want) != cudaSuccess) {
+    cudaGetLastError();
     return NEOGEMM_ERR_WORKSPACE;
   }
+  if (cudaMemset(fresh, 0, want) != cudaSuccess) {
+    cudaGetLastError();
+    cudaFree(fresh);
+    return NEOGEMM_ERR_WORKSPACE;
+  }
+  if (st->workspace != nullptr) st->retired_workspaces.push_back(st->workspace);
+  st->workspace = fresh;
   st->workspace_bytes = want;
   return NEOGEMM_OK;
 }
@@ -745,7 +764,7 @@ int gemm_device(const void* A, const void* B, void* C, int64_t M, int64_t N, int
         return NEOGEMM_ERR_WORKSPACE;
     } else {
       std::lock_guard<std::mutex> lock(g_mu);
-      rc = ensure_workspace(st, need);
+      rc = ensure_workspace(st, need, stream);
       if (rc != NEOGEMM_OK) return rc;
       ws = static_cast<char*>(st->workspace);
     }
@@ -868,6 +887,13 @@ int neogemm_bf16_nt_host(const void* A_host, const void* B_host, void* C_host, i
     std::lock_guard<std::mutex> lock(g_mu);
     st = device_state(&rc);
     if (st == nullptr) return rc;
+  }
+  // The staging buffers, the two copy queues and their events are one set per device: a second
+  // host thread calling in on the same device waits here until the first call has returned (the
+  // call is synchronous anyway).
+  std::lock_guard<std::mutex> one_call(st->host_entry_mu);
+  {
+    std::lock_guard<std::mutex> lock(g_mu);
     if ((rc = ensure_stage(st, 0, std::max<size_t>(bytes_a, 16))) != NEOGEMM_OK) return rc;
     if ((rc = ensure_stage(st, 1, std::max<size_t>(bytes_b, 16))) != NEOGEMM_OK) return rc;
     if ((rc = ensure_stage(st, 2, bytes_c)) != NEOGEMM_OK) return rc;
@@ -1132,6 +1158,12 @@ int neogemm_debug_plan(int64_t M, int64_t N, int64_t K, int64_t ldc, int c_col_m
 // (a pinned status word) and whenever a skinny shape needs a larger library-owned stream-K
 // workspace; this variant never does.  Its stream-K scratch is the fixed array below, which
 // every GPU that loads the library carries until the process exits.
+//
+// What "nothing" covers: no call below reaches cudaMalloc, cudaFree, cudaHostAlloc or an
+// allocating library routine.  What it cannot cover is the CUDA driver's own lazy loading: the
+// first use of the library's code on a device makes the driver place the module (the 32 MiB array
+// and the kernels) in device memory.  neogemm_noalloc_init() forces all of that to happen at a
+// moment the caller chooses - before its pool takes the device.
 // ------------------------------------------------------------------------------------------
 namespace {
 
@@ -1140,10 +1172,11 @@ static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBy
 static __device__ __align__(16) int g_static_status[4];
 
 struct StaticState {
-  bool ready = false;
-  int init_error = NEOGEMM_OK;
+  bool ready = false;                 // set only once the whole set-up has succeeded
+  bool warmed = false;                // every kernel variant loaded and configured
   unsigned char* scratch = nullptr;   // DEVICE address of g_static_scratch on this device
   int* status = nullptr;              // DEVICE address of g_static_status on this device
+  int seen[4] = {0, 0, 0, 0};         // the device status word as the host last read it
   DeviceState launch_state;           // only sm_count and the per-kernel attribute flags are used
 };
 StaticState g_static[kMaxDevices];
@@ -1151,7 +1184,8 @@ PFN_cuTensorMapEncodeTiled_v12000 g_static_encode = nullptr;
 
 // In host code the names g_static_scratch / g_static_status are host-side stand-ins, not device
 // addresses; the addresses a kernel may use come from cudaGetSymbolAddress, once per device,
-// with that device current.  Called with g_mu held.
+// with that device current.  Called with g_mu held.  A failed attempt is not remembered: a
+// transient error (the device had no room for the module at that moment) can be retried.
 StaticState* static_state(int* code) {
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
@@ -1161,18 +1195,19 @@ StaticState* static_state(int* code) {
   }
   StaticState& st = g_static[dev];
   if (st.ready) {
-    *code = st.init_error;
-    return st.init_error == NEOGEMM_OK ? &st : nullptr;
+    *code = NEOGEMM_OK;
+    return &st;
   }
-  st.ready = true;
   int major = 0;
   if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess ||
       major != 10 ||
       cudaDeviceGetAttribute(&st.launch_state.sm_count, cudaDevAttrMultiProcessorCount, dev) !=
           cudaSuccess) {
     cudaGetLastError();
-    st.init_error = NEOGEMM_ERR_UNSUPPORTED;
-  } else if (g_static_encode == nullptr) {
+    *code = NEOGEMM_ERR_UNSUPPORTED;
+    return nullptr;
+  }
+  if (g_static_encode == nullptr) {
     void* fn = nullptr;
     cudaDriverEntryPointQueryResult q;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) ==
@@ -1180,24 +1215,24 @@ StaticState* static_state(int* code) {
       g_static_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
     } else {
       cudaGetLastError();
-      st.init_error = NEOGEMM_ERR_DESCRIPTOR;
+      *code = NEOGEMM_ERR_DESCRIPTOR;
+      return nullptr;
     }
   }
-  if (st.init_error == NEOGEMM_OK) {
-    void* scratch = nullptr;
-    void* status = nullptr;
-    if (cudaGetSymbolAddress(&scratch, g_static_scratch) != cudaSuccess ||
-        cudaGetSymbolAddress(&status, g_static_status) != cudaSuccess || scratch == nullptr ||
-        status == nullptr) {
-      cudaGetLastError();
-      st.init_error = NEOGEMM_ERR_CUDA;
-    } else {
-      st.scratch = static_cast<unsigned char*>(scratch);
-      st.status = static_cast<int*>(status);
-    }
+  void* scratch = nullptr;
+  void* status = nullptr;
+  if (cudaGetSymbolAddress(&scratch, g_static_scratch) != cudaSuccess ||
+      cudaGetSymbolAddress(&status, g_static_status) != cudaSuccess || scratch == nullptr ||
+      status == nullptr) {
+    cudaGetLastError();
+    *code = NEOGEMM_ERR_CUDA;
+    return nullptr;
   }
-  *code = st.init_error;
-  return st.init_error == NEOGEMM_OK ? &st : nullptr;
+  st.scratch = static_cast<unsigned char*>(scratch);
+  st.status = static_cast<int*>(status);
+  st.ready = true;
+  *code = NEOGEMM_OK;
+  return &st;
 }
 
 // Same geometry as get_tensor_map(), encoded straight into the caller's variable: no cache, so no
@@ -1223,6 +1258,92 @@ int encode_map_uncached(const void* base, uint64_t inner, uint64_t rows, uint64_
 
 }  // namespace
 
+int neogemm_noalloc_init(void) {
+  std::lock_guard<std::mutex> lock(g_mu);
+  int rc;
+  StaticState* st = static_state(&rc);
+  if (st == nullptr) return rc;
+  if (st->warmed) return NEOGEMM_OK;
+  // Configuring a kernel makes the driver load it: after this loop no shape can meet a variant
+  // that still has to be placed on the device.
+  int n;
+  const KernelEntry* table = kernel_table(&n);
+  for (int i = 0; i < n; ++i) {
+    if (st->launch_state.attr_done[i]) continue;
+    if (cudaFuncSetAttribute(table[i].fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             table[i].smem_bytes) != cudaSuccess) {
+      cudaGetLastError();
+      return NEOGEMM_ERR_LAUNCH;
+    }
+    st->launch_state.attr_done[i] = true;
+  }
+  cudaFuncAttributes unused;
+  if (cudaFuncGetAttributes(&unused, reinterpret_cast<const void*>(
+                                         &wait_expiry_selftest_kernel)) != cudaSuccess) {
+    cudaGetLastError();
+    return NEOGEMM_ERR_LAUNCH;
+  }
+  if (cudaMemset(st->status, 0, sizeof(int) * 4) != cudaSuccess) {
+    cudaGetLastError();
+    return NEOGEMM_ERR_CUDA;
+  }
+  st->warmed = true;
+  return NEOGEMM_OK;
+}
+
+int neogemm_noalloc_status(int out[4], void* stream_) {
+  if (out == nullptr) return NEOGEMM_ERR_BAD_ARG;
+  std::lock_guard<std::mutex> lock(g_mu);
+  int rc;
+  StaticState* st = static_state(&rc);
+  if (st == nullptr) return rc;
+  // The word lives in device memory: wait for the caller's launches, then copy 16 bytes into the
+  // caller's array.  Nothing is allocated; the copy is synchronous.
+  int word[4] = {0, 0, 0, 0};
+  if (cudaStreamSynchronize(static_cast<cudaStream_t>(stream_)) != cudaSuccess ||
+      cudaMemcpy(word, st->status, sizeof(word), cudaMemcpyDeviceToHost) != cudaSuccess) {
+    cudaGetLastError();
+    return NEOGEMM_ERR_CUDA;
+  }
+  for (int i = 0; i < 4; ++i) out[i] = st->seen[i] = word[i];
+  return NEOGEMM_OK;
+}
+
+int neogemm_noalloc_clear_status(void) {
+  std::lock_guard<std::mutex> lock(g_mu);
+  int rc;
+  StaticState* st = static_state(&rc);
+  if (st == nullptr) return rc;
+  // A launch that gave up may also have left arrival counters of the fixed scratch non-zero;
+  // every call clears those before it launches, so only the status word needs attention here.
+  if (cudaDeviceSynchronize() != cudaSuccess ||
+      cudaMemset(st->status, 0, sizeof(int) * 4) != cudaSuccess) {
+    cudaGetLastError();
+    return NEOGEMM_ERR_CUDA;
+  }
+  for (int i = 0; i < 4; ++i) st->seen[i] = 0;
+  return NEOGEMM_OK;
+}
+
+int neogemm_debug_wait_expiry_noalloc(unsigned int limit_us) {
+  if (limit_us == 0 || limit_us > 100000) return NEOGEMM_ERR_BAD_ARG;
+  std::lock_guard<std::mutex> lock(g_mu);
+  int rc;
+  StaticState* st = static_state(&rc);
+  if (st == nullptr) return rc;
+  GemmParams params;
+  std::memset(&params, 0, sizeof(params));
+  params.status = st->status;
+  wait_expiry_selftest_kernel<<<1, 32>>>(params, static_cast<unsigned long long>(limit_us) * 1000ull,
+                                         nullptr);
+  if (cudaGetLastError() != cudaSuccess) return NEOGEMM_ERR_LAUNCH;
+  if (cudaDeviceSynchronize() != cudaSuccess) {
+    cudaGetLastError();
+    return NEOGEMM_ERR_CUDA;
+  }
+  return NEOGEMM_OK;
+}
+
 int neogemm_bf16_nt_noalloc(const void* A, const void* B, void* C, int64_t M, int64_t N,
                             int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int c_col_major,
                             void* stream_) {
@@ -1234,6 +1355,9 @@ int neogemm_bf16_nt_noalloc(const void* A, const void* B, void* C, int64_t M, in
   std::lock_guard<std::mutex> lock(g_mu);
   StaticState* st = static_state(&rc);
   if (st == nullptr) return rc;
+  // An error a launch of this entry point recorded on the device, as last read back by
+  // neogemm_noalloc_status(): refuse until neogemm_noalloc_clear_status().
+  if (st->seen[0] != 0) return NEOGEMM_ERR_DEVICE_TIMEOUT;
 
   const int64_t pm = c_col_major ? N : M;
   const int64_t pn = c_col_major ? M : N;
@@ -1254,7 +1378,7 @@ int neogemm_bf16_nt_noalloc(const void* A, const void* B, void* C, int64_t M, in
   const Override no_override;
   // Only the skinny (direct-store) kernels take scratch here: the cut last wave of the large
   // kernels is left off, so that large shapes never depend on the fixed array's size.
-  rc = make_plan(pm, pn, K, ldc, C, st->launch_state.sm_count, no_override, &plan, false);
+  rc = make_plan(pm, pn, K, ldc, C, st->launch_state.sm_count, no_override, &plan, false, true);
   if (rc != NEOGEMM_OK) return rc;
   if (plan.stream_k && plan.counters_bytes + plan.partials_bytes > kStaticScratchBytes)
     return NEOGEMM_ERR_WORKSPACE;   // beyond the fixed scratch: use neogemm_bf16_nt()
@@ -1291,6 +1415,7 @@ int neogemm_bf16_nt_noalloc(const void* A, const void* B, void* C, int64_t M, in
   params.l2_hints = (plan.epi == kEpiDirect && plan.num_n_tiles == 1) ? 24 : kDefaultTuning[0];
   params.epi_wait_hint_ns = kDefaultTuning[1];
   params.main_wait_hint_ns = kDefaultTuning[2];
+  params.wide_prologue = kDefaultWidePrologue;
   params.out = static_cast<__nv_bfloat16*>(C);
   params.out_stride_r = plan.swap ? 1 : ldc;
   params.out_stride_c = plan.swap ? ldc : 1;
@@ -1318,6 +1443,14 @@ int neogemm_bf16_nt_noalloc(const void* A, const void* B, void* C, int64_t M, in
     params.partials_elems = static_cast<long long>(plan.partials_bytes / sizeof(float));
     params.dyn_counter = reinterpret_cast<int*>(st->scratch) + params.counters_len;
   }
+  t_last_config[0] = plan.cta_group;
+  t_last_config[1] = plan.block_n * plan.halves;
+  t_last_config[2] = plan.kernel->stages;
+  t_last_config[3] = plan.swap ? 1 : 0;
+  t_last_config[4] = plan.stream_k ? 1 : 0;
+  t_last_config[5] = plan.num_ctas;
+  t_last_config[6] = plan.num_tiles;
+  t_last_config[7] = plan.group_m;
   return launch(&st->launch_state, plan, mx, my, md, params, stream);
 }
 

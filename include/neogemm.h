@@ -93,21 +93,52 @@ int neogemm_bf16_nt_fused(const void* A, const void* B, void* C,
  * libneogemm.so holds until the process exits.
  *
  * Arguments as for neogemm_bf16_nt(), without the workspace pair.  Differences:
- *   - a shape whose stream-K scratch would exceed the 32 MiB returns NEOGEMM_ERR_WORKSPACE
- *     (the benchmark's largest skinny shape, M=128 N=28672 K=8192, needs 29.6 MiB and fits);
+ *   - a shape whose stream-K scratch (256 KiB of counters + one fp32 partial tile per contributor
+ *     of every cut tile) would exceed the 32 MiB returns NEOGEMM_ERR_WORKSPACE.  That is not only
+ *     very long skinny shapes: a large result that cannot take the TMA-store kernels (packed
+ *     row-major C with N % 8 != 0, e.g. 8192 x 1001) is planned as cut 128 x 128 tiles and is
+ *     refused as well - use neogemm_bf16_nt() for those.  The benchmark's decode shapes
+ *     (M <= 128, N = 28672, K = 8192) run as one wave of whole tiles and need no scratch at all;
+ *     64 x 3584 x 2048 uses 3.8 MiB of it, 16 x 40960 x 4096 (cut tiles plus run-time claimed
+ *     pieces) 7.8 MiB;
  *   - the first call on each device looks up the device address of the array
- *     (cudaGetSymbolAddress) and the driver's tensor-map encoder; make that first call before
- *     starting any stream capture;
+ *     (cudaGetSymbolAddress) and the driver's tensor-map encoder; make that first call - or
+ *     neogemm_noalloc_init() - before starting any stream capture;
+ *   - the CUDA driver loads a library's code and static data onto a device lazily, on first use.
+ *     That first use (32 MiB plus the kernels) needs device memory that this library never asks
+ *     for but the driver does: call neogemm_noalloc_init() BEFORE the pool takes the device.  A
+ *     set-up that failed is retried on the next call, it is not remembered;
  *   - all calls on a device share the one array: calls whose kernels may overlap on the GPU
  *     (different streams) race on it - serialise them, or use neogemm_bf16_nt() with separate
  *     workspaces.  The part that must start at zero is cleared in stream order by every call;
- *   - device-side bounded-wait failures are recorded in a word inside the library that
- *     neogemm_device_status() does not show; thread-local overrides and tuning knobs are ignored.
+ *   - device-side errors (an expired bounded wait, an index that failed the kernel's own bounds
+ *     check) are recorded in a word in DEVICE memory, which neogemm_device_status() does not
+ *     show: read it with neogemm_noalloc_status().  Once that has seen an error, this entry point
+ *     returns NEOGEMM_ERR_DEVICE_TIMEOUT until neogemm_noalloc_clear_status();
+ *   - thread-local overrides and tuning knobs are ignored; neogemm_last_config() reports the
+ *     plan of the most recent call as usual.
  */
 int neogemm_bf16_nt_noalloc(const void* A, const void* B, void* C,
                             int64_t M, int64_t N, int64_t K,
                             int64_t lda, int64_t ldb, int64_t ldc,
                             int c_col_major, void* stream);
+
+/* Companions of neogemm_bf16_nt_noalloc(); none of them allocates.  (No counterpart in the
+ * reference.)
+ *
+ * neogemm_noalloc_init(): makes the driver load everything the entry point can ever launch on the
+ *   current device - the fixed scratch array, its status word and every kernel variant - and
+ *   zeroes the status word.  Call it once per device while device memory is still available
+ *   (before the caller's pool claims it) and before any stream capture; afterwards no shape can
+ *   meet a kernel that still has to be placed on the device.  Synchronous.  Safe to repeat.
+ * neogemm_noalloc_status(out, stream): waits for `stream`, then copies the device-side error
+ *   record of the entry point into out[4] (same fields as neogemm_device_status()).  Synchronous;
+ *   meant for the end of a batch or a health check, not for every call.
+ * neogemm_noalloc_clear_status(): waits for the device, clears the record, re-opens the entry
+ *   point after an error. */
+int neogemm_noalloc_init(void);
+int neogemm_noalloc_status(int out[4], void* stream);
+int neogemm_noalloc_clear_status(void);
 
 /* Upper bound on the workspace neogemm_bf16_nt() may need for this shape on the current device
  * (0 when the data-parallel schedule would be chosen).  No counterpart in the reference, which
@@ -217,6 +248,11 @@ int neogemm_debug_plan(int64_t M, int64_t N, int64_t K, int64_t ldc, int c_col_m
  * (nullable) receives the time the warp actually waited.  Synchronous.  The reference has no
  * error path to test (nemgemmV03.cu:387-390 prints cudaGetLastError). */
 int neogemm_debug_wait_expiry(unsigned int limit_us, unsigned long long* waited_ns_out);
+
+/* The same self-test aimed at the error record of neogemm_bf16_nt_noalloc(): afterwards
+ * neogemm_noalloc_status() shows code 4 and that entry point returns NEOGEMM_ERR_DEVICE_TIMEOUT
+ * until neogemm_noalloc_clear_status().  Allocates nothing.  Synchronous. */
+int neogemm_debug_wait_expiry_noalloc(unsigned int limit_us);
 
 /* Library version, e.g. 100 = 1.0.0. */
 int neogemm_version(void);

@@ -1,6 +1,6 @@
 """Launched by torchrun (one rank per GPU): parity of the row-sharded product on real GPUs.
 Each rank builds the same seeded problem on the CPU, takes its row block of A, receives B by NCCL
-broadcast (plain and chunk-overlapped variants) and checks its rows of C against the CPU oracle,
+broadcast (plain, chunk-overlapped and host-buffer pipeline variants) and checks its rows of C against the CPU oracle,
 and B against the original bits.  Exit status 0 = every rank passed."""
 import os
 import sys
@@ -13,7 +13,8 @@ import torch.distributed as dist  # noqa: E402
 
 from gemm_b200 import ops  # noqa: E402
 from gemm_b200.inputs import make_problem  # noqa: E402
-from gemm_b200.shard import row_partition, sharded_matmul, sharded_matmul_overlapped  # noqa: E402
+from gemm_b200.shard import (row_partition, sharded_matmul, sharded_matmul_host,  # noqa: E402
+                             sharded_matmul_overlapped)
 from oracle import oracle  # noqa: E402
 
 
@@ -36,6 +37,15 @@ def main():
             assert ops.device_status()[0] == 0
             assert torch.equal(B_local.cpu().view(torch.int16), B.view(torch.int16)), name
             oracle.assert_parity(C_block, ref, f"{name} rank {rank}/{world}")
+        # host buffers in and out: uploads, broadcast, products and downloads overlapped
+        hA = A[r0:r1].contiguous().pin_memory()
+        hB = B.pin_memory() if rank == 0 else None
+        hC = torch.full((r1 - r0, N), float("nan"), dtype=torch.bfloat16).pin_memory()
+        for call in range(2):
+            sharded_matmul_host(hA, hB, hC, N, K)
+            assert ops.device_status()[0] == 0
+            oracle.assert_parity(hC, ref, f"host pipeline call {call} rank {rank}/{world}")
+            hC.fill_(float("nan"))
         C_full, _ = sharded_matmul(A_block, B_dev, N, K, gather=True)
         oracle.assert_parity(C_full, oracle.gemm_fp32(A, B), f"gathered rank {rank}")
         print(f"rank {rank}: sharded parity ok", flush=True)

@@ -121,6 +121,55 @@ def test_overlapped_broadcast_on_two_gloo_ranks(tmp_path):
     assert all((tmp_path / f"ok{r}").exists() for r in range(world))
 
 
+def _worker_host_pipeline(rank, world, port, M, N, K, out_dir):
+    import torch.distributed as dist
+    from gemm_b200.inputs import make_problem
+    from gemm_b200.shard import ShardedHostPipeline, row_partition, sharded_matmul_host
+    from oracle import oracle
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        A, B = make_problem(M, N, K, seed=8)
+        r0, r1 = row_partition(M, world, rank)
+        calls = []
+
+        def stand_in(a, b, out):
+            calls.append(tuple(a.shape))
+            out.copy_(oracle.gemm_bf16(a.contiguous(), b.contiguous()))
+        hC = torch.full((r1 - r0, N), float("nan"), dtype=torch.bfloat16)
+        sharded_matmul_host(A[r0:r1].contiguous(), B if rank == 0 else None, hC, N, K,
+                            device="cpu", matmul_out=stand_in)
+        want = oracle.gemm_bf16(A, B)[r0:r1].contiguous()
+        assert torch.equal(hC.view(torch.int16), want.view(torch.int16)), "host pipeline rows of C"
+        # explicit chunking: three row chunks on 256-row boundaries, two chunks of B
+        pipe = ShardedHostPipeline(r1 - r0, N, K, "cpu", row_chunks=3, b_chunks=2,
+                                   matmul_out=stand_in)
+        assert all(a % 256 == 0 for a, _ in pipe.a_bounds) and pipe.a_bounds[-1][1] == r1 - r0
+        assert pipe.b_bounds[0][0] == 0 and pipe.b_bounds[-1][1] == N
+        calls.clear()
+        hC.fill_(float("nan"))
+        pipe.run(A[r0:r1].contiguous(), B if rank == 0 else None, hC)
+        assert len(calls) == len(pipe.a_bounds) and sum(c[0] for c in calls) == r1 - r0
+        assert torch.equal(hC.view(torch.int16), want.view(torch.int16))
+        assert torch.equal(pipe.dB.view(torch.int16), B.view(torch.int16)), "broadcast of B"
+        assert pipe.h2d_bytes(rank) == (r1 - r0) * K * 2 + (N * K * 2 if rank == 0 else 0)
+        if rank == 0:
+            with pytest.raises(ValueError):
+                pipe.run(A[r0:r1].contiguous(), None, hC)
+        open(os.path.join(out_dir, f"ok{rank}"), "w").close()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(180)
+def test_host_pipeline_on_two_gloo_ranks(tmp_path):
+    world = 2
+    mp.spawn(_worker_host_pipeline, args=(world, _free_port(), 1500, 520, 64, str(tmp_path)),
+             nprocs=world, join=True)
+    assert all((tmp_path / f"ok{r}").exists() for r in range(world))
+
+
 @pytest.mark.gpu
 @pytest.mark.timeout(600)
 def test_sharded_product_on_the_gpus_of_this_box():

@@ -41,3 +41,29 @@ def run_case(M, N, K, col_major=False, seed=1234, override=None, scale_by_k=True
     label = what or f"{M}x{N}x{K} col_major={col_major} cfg={cfg}"
     stats = oracle.assert_parity(out, ref, label, **gates)
     return stats, cfg
+
+
+def gpu_bits_compare(out: torch.Tensor, other: torch.Tensor) -> dict:
+    """Bit-level comparison of two bf16 matrices ON THE GPU (both results of a GPU kernel, e.g.
+    ours and cuBLAS'): fraction of bit-equal elements and the largest distance in bf16 ulps.
+    Elements within 2^-6 of the RMS magnitude of zero are judged by absolute error, as in
+    oracle.compare (an ulp next to zero means nothing)."""
+    assert out.is_cuda and other.is_cuda and out.dtype == other.dtype == torch.bfloat16
+    assert out.shape == other.shape
+    def key(t):
+        b = t.contiguous().view(torch.int16).to(torch.int32) & 0xFFFF
+        return torch.where(b >= 0x8000, 0x8000 - b, b)
+    ulp = (key(out) - key(other)).abs()
+    r = other.float()
+    rms = float(r.double().pow(2).mean().sqrt()) if r.numel() else 0.0
+    small = r.abs() < rms * 2.0 ** -6
+    big_ulp = ulp[~small]
+    small_err = (out.float() - r).abs()[small]
+    return {
+        "finite": bool(torch.isfinite(out).all()) and bool(torch.isfinite(other).all()),
+        "bit_equal_frac": float((ulp == 0).float().mean()) if ulp.numel() else 1.0,
+        "max_ulp": int(big_ulp.max()) if big_ulp.numel() else 0,
+        "near_zero_ok": bool((small_err <= rms * 2.0 ** -6 * 2.0 ** -7).all())
+        if small_err.numel() else True,
+        "elements": int(ulp.numel()),
+    }
