@@ -41,6 +41,8 @@ def _load() -> ctypes.CDLL:
                                           c_int64, c_int64, c_int64, c_int, ctypes.c_float,
                                           ctypes.c_float, c_void_p, c_int, c_void_p, c_size_t,
                                           c_void_p]
+    lib.neogemm_bf16_nt_fused_f32.restype = c_int
+    lib.neogemm_bf16_nt_fused_f32.argtypes = list(lib.neogemm_bf16_nt_fused.argtypes)
     lib.neogemm_bf16_nt_noalloc.restype = c_int
     lib.neogemm_bf16_nt_noalloc.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                             c_int64, c_int64, c_int64, c_int64, c_int, c_void_p]

@@ -68,6 +68,12 @@ struct GemmParams {
   int k_alternate;
   // Direct epilogue / split partials.
   __nv_bfloat16* out;
+  // fp32 result (fused entry point only): when non-null the epilogue writes the unrounded fp32
+  // values here instead of bf16 to `out`, with the same strides (in elements), and reads the
+  // beta term from c_in32.  Two-half tiles do not take this path (the launcher never picks them
+  // for an fp32 result).
+  float* out32;
+  const float* c_in32;
   long long out_stride_r, out_stride_c;
   // Stream-K (zero / null in the data-parallel schedule).
   int stream_k;              // 1: tiles >= sk_first_tile are cut: CTA c owns units [c*U/G, (c+1)*U/G)
@@ -475,21 +481,28 @@ struct WorkSource {
 
 // Fused epilogue on kN consecutive columns [col, col + kN) of one row of D held in r[] (fp32
 // bit patterns), in place.  Reads of C_in and bias are bounds-checked against Md / Nd.
-template <int kN>
+// kF32: the instantiation may be asked for an fp32 result (beta term read from c_in32); kernels
+// that never are (two-half tiles) compile the branch out, it would only cost them registers.
+template <int kN, bool kF32 = true>
 __device__ __forceinline__ void fused_epilogue(uint32_t (&r)[kN], const GemmParams& p, int row,
                                                int col) {
   const bool row_ok = row < p.Md;
   float row_bias = 0.f;
   if (p.bias != nullptr && p.bias_on_rows && row_ok) row_bias = __bfloat162float(p.bias[row]);
   const __nv_bfloat16* cin = nullptr;
-  if (p.beta != 0.f && row_ok)
-    cin = p.c_in + static_cast<long long>(row) * p.out_stride_r;
+  const float* cin32 = nullptr;
+  if (p.beta != 0.f && row_ok) {
+    if (kF32 && p.c_in32 != nullptr) cin32 = p.c_in32 + static_cast<long long>(row) * p.out_stride_r;
+    else cin = p.c_in + static_cast<long long>(row) * p.out_stride_r;
+  }
 #pragma unroll
   for (int j = 0; j < kN; ++j) {
     float v = p.alpha * __uint_as_float(r[j]);
     const bool ok = row_ok && (col + j) < p.Nd;
     if (cin != nullptr && ok)
       v += p.beta * __bfloat162float(cin[static_cast<long long>(col + j) * p.out_stride_c]);
+    if (kF32 && cin32 != nullptr && ok)
+      v += p.beta * cin32[static_cast<long long>(col + j) * p.out_stride_c];
     if (p.bias != nullptr && ok)
       v += p.bias_on_rows ? row_bias : __bfloat162float(p.bias[col + j]);
     if (p.activation == 1) {
@@ -1041,10 +1054,10 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
             else mbar_arrive(tmem_empty_bar);
           }
           if (p.fuse) {
-            fused_epilogue<32>(ra, p, row0 + row_in_cta, c_half);
-            fused_epilogue<32>(rb, p, row0 + row_in_cta, c_half + 32);
-            fused_epilogue<32>(rc, p, row0 + row_in_cta, c_half + 64);
-            fused_epilogue<32>(rd, p, row0 + row_in_cta, c_half + 96);
+            fused_epilogue<32, false>(ra, p, row0 + row_in_cta, c_half);
+            fused_epilogue<32, false>(rb, p, row0 + row_in_cta, c_half + 32);
+            fused_epilogue<32, false>(rc, p, row0 + row_in_cta, c_half + 64);
+            fused_epilogue<32, false>(rd, p, row0 + row_in_cta, c_half + 96);
           }
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
@@ -1075,8 +1088,8 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
                 }
               }
               if (p.fuse) {
-                fused_epilogue<32>(ra, p, row0 + row_in_cta, c_half + bt * 64);
-                fused_epilogue<32>(rb, p, row0 + row_in_cta, c_half + bt * 64 + 32);
+                fused_epilogue<32, false>(ra, p, row0 + row_in_cta, c_half + bt * 64);
+                fused_epilogue<32, false>(rb, p, row0 + row_in_cta, c_half + bt * 64 + 32);
               }
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
@@ -1171,8 +1184,39 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
             fused_epilogue<32>(r0, p, row0 + row_in_cta, col0 + c);
             fused_epilogue<32>(r1, p, row0 + row_in_cta, col0 + c + 32);
           }
-          const uint32_t row_addr = buf + lane * 128u;
           const uint32_t sw = lane & 7u;
+          if (p.out32 != nullptr) {
+            // fp32 result: a box is 32 rows x 32 columns (128 B per row), so each 64-column step
+            // leaves as two boxes, r0 and r1, each through a staging buffer of its own: the
+            // step's regular buffer and - for r1 - the other regular buffer (one-half tiles have
+            // two per warp), or the next ring slot when the ring is free.
+#pragma unroll
+            for (int hb = 0; hb < 2; ++hb) {
+              const uint32_t fbuf = ring_is_free
+                  ? ring + static_cast<uint32_t>(((warp - 2) * kBoxes + i) * 2 + hb) * Cfg::SMEM_EPI_WARP_BUF
+                  : warp_stage + static_cast<uint32_t>(hb) * Cfg::SMEM_EPI_WARP_BUF;
+              // Buffer hb was last read by the store issued two groups ago: all but the most
+              // recent group must have finished reading (hb == 0 was waited for above).
+              if (!ring_is_free && hb == 1 && lane == 0) tma_store_wait_read<1>();
+              __syncwarp();
+              const uint32_t frow = fbuf + lane * 128u;
+              const uint32_t* src = hb == 0 ? r0 : r1;
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                st_shared_v4(frow + ((static_cast<uint32_t>(j) ^ sw) << 4), src[4 * j + 0],
+                             src[4 * j + 1], src[4 * j + 2], src[4 * j + 3]);
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                if (my_row0 < p.Md && col0 + c + 32 * hb < p.Nd)
+                  tma_store_2d(&tmap_d, fbuf, col0 + c + 32 * hb, my_row0);
+                tma_store_commit();
+              }
+            }
+            ++store_count;
+            continue;
+          }
+          const uint32_t row_addr = buf + lane * 128u;
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             st_shared_v4(row_addr + ((static_cast<uint32_t>(j) ^ sw) << 4),
@@ -1206,7 +1250,9 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
         const bool vec_ok = (p.out_stride_c == 1) && ((p.out_stride_r & 7) == 0) &&
                             ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
         // Transposed result (rows of D are contiguous in memory): stage, then 16-byte stores.
-        transposed = (p.out_stride_r == 1) && ((p.out_stride_c & 7) == 0) &&
+        // An fp32 result is never staged: with one row per lane, the 32 lanes' stores of one
+        // column are 128 contiguous bytes already.
+        transposed = (p.out32 == nullptr) && (p.out_stride_r == 1) && ((p.out_stride_c & 7) == 0) &&
                      ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
         const uint32_t stg = epi_base + (warp - 2) * Cfg::SMEM_EPI_T_WARP;
         // 32 columns per step where the tile has them: half as many dependent round trips to
@@ -1257,6 +1303,29 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
                 const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(v);
                 for (int j = 0; j < 8 && n0 + j < p.Md; ++j) {
                   if (off + j < p.out_span) p.out[off + j] = e[j];
+                }
+              }
+            }
+          } else
+          if (p.out32 != nullptr) {
+            if (row < p.Md && col < p.Nd) {
+              const int last_col = min(col + kDC - 1, p.Nd - 1);
+              const long long last = static_cast<long long>(row) * p.out_stride_r +
+                                     static_cast<long long>(last_col) * p.out_stride_c;
+              float* out_row32 = p.out32 + static_cast<long long>(row) * p.out_stride_r;
+              if (last >= p.out_span) {
+                report_error(p, abort_flag, kDevBounds, seg_idx, 3);
+              } else if (p.out_stride_c == 1 && (p.out_stride_r & 3) == 0 && col + kDC <= p.Nd &&
+                         (reinterpret_cast<uintptr_t>(p.out32) & 15) == 0) {
+#pragma unroll
+                for (int v4 = 0; v4 < kDC / 4; ++v4)
+                  *reinterpret_cast<uint4*>(out_row32 + col + 4 * v4) =
+                      make_uint4(r[4 * v4 + 0], r[4 * v4 + 1], r[4 * v4 + 2], r[4 * v4 + 3]);
+              } else {
+#pragma unroll
+                for (int j = 0; j < kDC; ++j) {
+                  if (col + j < p.Nd)
+                    out_row32[static_cast<long long>(col + j) * p.out_stride_c] = __uint_as_float(r[j]);
                 }
               }
             }

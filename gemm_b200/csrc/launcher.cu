@@ -246,8 +246,9 @@ constexpr size_t kMapCacheSize = 128;
 // box height following the tile instead of the fixed 64.
 int get_tensor_map(const void* base, uint64_t inner, uint64_t rows, uint64_t pitch_bytes,
                    uint32_t box_rows, int for_store, CUtensorMap* out) {
-  // for_store: 1 = store map (no promotion); loads: 0 = 256-byte L2 promotion (default),
-  // -1 none, -2 64 B, -3 128 B (tuning key 5).
+  // for_store: 1 = store map (no promotion), 2 = store map of an fp32 matrix (`inner` fp32
+  // elements per row, box 32 x box_rows: again one 128-byte swizzle row); loads: 0 = 256-byte L2
+  // promotion (default), -1 none, -2 64 B, -3 128 B (tuning key 5).
   const MapKey key{base, inner, rows, pitch_bytes, box_rows, for_store};
   for (size_t i = t_map_cache.size(); i-- > 0;) {
     if (t_map_cache[i].key == key) {
@@ -262,13 +263,14 @@ int get_tensor_map(const void* base, uint64_t inner, uint64_t rows, uint64_t pit
   }
   cuuint64_t dims[2] = {inner, rows};
   cuuint64_t strides[1] = {pitch_bytes};
-  cuuint32_t box[2] = {64, box_rows};
+  cuuint32_t box[2] = {for_store == 2 ? 32u : 64u, box_rows};
   cuuint32_t elem_strides[2] = {1, 1};
   CUtensorMap m;
   const CUresult r = g_encode(
-      &m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+      &m, for_store == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+      const_cast<void*>(base), dims, strides, box,
       elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-      for_store == 1 ? CU_TENSOR_MAP_L2_PROMOTION_NONE
+      for_store >= 1 ? CU_TENSOR_MAP_L2_PROMOTION_NONE
       : for_store == -1 ? CU_TENSOR_MAP_L2_PROMOTION_NONE
       : for_store == -2 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
       : for_store == -3 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B
@@ -325,9 +327,11 @@ int hybrid_splits(int rest, int workers, int num_k_blocks, int min_chunk = 8) {
 // pm x pn is the matrix as stored (row-major, pitch ldc): [M,N] for row-major C, [N,M] for the
 // reference's column-major C.
 int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int sm_count,
-              const Override& ov, Plan* plan, bool allow_hybrid = true, bool allow_dyn_pool = true) {
+              const Override& ov, Plan* plan, bool allow_hybrid = true, bool allow_dyn_pool = true,
+              int c_elem_bytes = 2) {
   Plan p;
-  const bool tma_store_ok = (ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
+  const bool tma_store_ok = ((ldc * c_elem_bytes) % 16 == 0) &&
+                            ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
 
   // Orientation.  The 128-lane axis of the tensor core wants the long dimension.
   bool swap = (pm <= 128 && pn > pm);
@@ -538,7 +542,7 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
 }
 
 int validate(const void* A, const void* B, const void* C, int64_t M, int64_t N, int64_t K,
-             int64_t lda, int64_t ldb, int64_t ldc, int c_col_major) {
+             int64_t lda, int64_t ldb, int64_t ldc, int c_col_major, int c_elem_bytes = 2) {
   if (M < 0 || N < 0 || K < 0) return NEOGEMM_ERR_BAD_ARG;
   if (M == 0 || N == 0) return NEOGEMM_OK;
   if (C == nullptr) return NEOGEMM_ERR_BAD_ARG;
@@ -549,7 +553,8 @@ int validate(const void* A, const void* B, const void* C, int64_t M, int64_t N, 
   if (K % 8 != 0 || lda % 8 != 0 || ldb % 8 != 0) return NEOGEMM_ERR_UNSUPPORTED;
   if ((reinterpret_cast<uintptr_t>(A) & 15) != 0 || (reinterpret_cast<uintptr_t>(B) & 15) != 0)
     return NEOGEMM_ERR_UNSUPPORTED;
-  if ((reinterpret_cast<uintptr_t>(C) & 1) != 0) return NEOGEMM_ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(C) & static_cast<uintptr_t>(c_elem_bytes - 1)) != 0)
+    return NEOGEMM_ERR_UNSUPPORTED;
   if (M > 0x7fffffffll || N > 0x7fffffffll || K > 0x7fffffffll) return NEOGEMM_ERR_UNSUPPORTED;
   return NEOGEMM_OK;
 }
@@ -627,12 +632,14 @@ struct Fusion {
   float alpha = 1.f, beta = 0.f;
   const void* bias = nullptr;   // bf16[N] or null
   int activation = 0;           // 0 none, 1 ReLU, 2 GELU (tanh form)
+  bool out_f32 = false;         // C holds fp32: the result is stored unrounded
 };
 
 int gemm_device(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
                 int64_t lda, int64_t ldb, int64_t ldc, int c_col_major, void* workspace,
                 size_t workspace_bytes, cudaStream_t stream, const Fusion& fusion = Fusion()) {
-  int rc = validate(A, B, C, M, N, K, lda, ldb, ldc, c_col_major);
+  const int c_elem = fusion.out_f32 ? 4 : 2;
+  int rc = validate(A, B, C, M, N, K, lda, ldb, ldc, c_col_major, c_elem);
   if (rc != NEOGEMM_OK) return rc;
   if (M == 0 || N == 0) return NEOGEMM_OK;
   if (fusion.on && K == 0) return NEOGEMM_ERR_UNSUPPORTED;
@@ -661,7 +668,9 @@ int gemm_device(const void* A, const void* B, void* C, int64_t M, int64_t N, int
   const int64_t ldv = c_col_major ? lda : ldb;
 
   Plan plan;
-  rc = make_plan(pm, pn, K, ldc, C, st->sm_count, t_override, &plan);
+  Override ov = t_override;
+  if (fusion.out_f32) ov.tuning[3] = 0;   // two-half tiles keep their result packed as bf16
+  rc = make_plan(pm, pn, K, ldc, C, st->sm_count, ov, &plan, true, true, c_elem);
   if (rc != NEOGEMM_OK) return rc;
 
   const void* X = plan.swap ? V : U;
@@ -683,7 +692,7 @@ int gemm_device(const void* A, const void* B, void* C, int64_t M, int64_t N, int
   if (rc != NEOGEMM_OK) return rc;
   if (plan.epi == kEpiTmaStore) {
     rc = get_tensor_map(C, static_cast<uint64_t>(plan.Nd), static_cast<uint64_t>(plan.Md),
-                        static_cast<uint64_t>(ldc) * 2, 32, 1, &md);
+                        static_cast<uint64_t>(ldc) * c_elem, 32, fusion.out_f32 ? 2 : 1, &md);
     if (rc != NEOGEMM_OK) return rc;
   }
 
@@ -743,6 +752,10 @@ int gemm_device(const void* A, const void* B, void* C, int64_t M, int64_t N, int
     params.alpha = fusion.alpha;
     params.beta = fusion.beta;
     params.c_in = static_cast<const __nv_bfloat16*>(C);
+    if (fusion.out_f32) {
+      params.out32 = static_cast<float*>(C);
+      params.c_in32 = static_cast<const float*>(C);
+    }
     params.bias = static_cast<const __nv_bfloat16*>(fusion.bias);
     // The bias runs along N.  N is the row axis of D when exactly one of "column-major C" and
     // "operands swapped" holds.
@@ -845,6 +858,23 @@ int neogemm_bf16_nt_fused(const void* A, const void* B, void* C, int64_t M, int6
   f.beta = beta;
   f.bias = bias;
   f.activation = activation;
+  return gemm_device(A, B, C, M, N, K, lda, ldb, ldc, c_col_major, workspace, workspace_bytes,
+                     static_cast<cudaStream_t>(stream), f);
+}
+
+int neogemm_bf16_nt_fused_f32(const void* A, const void* B, void* C, int64_t M, int64_t N,
+                              int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int c_col_major,
+                              float alpha, float beta, const void* bias, int activation,
+                              void* workspace, size_t workspace_bytes, void* stream) {
+  if (activation < 0 || activation > 2) return NEOGEMM_ERR_BAD_ARG;
+  if (bias != nullptr && (reinterpret_cast<uintptr_t>(bias) & 1) != 0) return NEOGEMM_ERR_BAD_ARG;
+  Fusion f;
+  f.on = true;
+  f.alpha = alpha;
+  f.beta = beta;
+  f.bias = bias;
+  f.activation = activation;
+  f.out_f32 = true;
   return gemm_device(A, B, C, M, N, K, lda, ldb, ldc, c_col_major, workspace, workspace_bytes,
                      static_cast<cudaStream_t>(stream), f);
 }

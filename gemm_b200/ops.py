@@ -107,18 +107,26 @@ ACTIVATIONS = {"none": 0, "relu": 1, "gelu_tanh": 2}
 
 def matmul_fused(A: torch.Tensor, B: torch.Tensor, out: Optional[torch.Tensor] = None,
                  alpha: float = 1.0, beta: float = 0.0, bias: Optional[torch.Tensor] = None,
-                 activation: str = "none", col_major: bool = False) -> torch.Tensor:
+                 activation: str = "none", col_major: bool = False,
+                 out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """out = act(alpha * A @ B^T + beta * out + bias), in fp32 on the accumulator, rounded once.
     ``bias`` is a bf16 vector of length N; ``out`` is required when beta != 0.  With
-    ``col_major`` the result is stored as neoGemmV1 stores it (``out`` is then [N,M])."""
+    ``col_major`` the result is stored as neoGemmV1 stores it (``out`` is then [N,M]).
+    ``out_dtype`` (or the dtype of ``out``) may be torch.float32: the result is then stored
+    unrounded, and the beta term is read as fp32."""
     M, N, K = _check_operands(A, B)
     shape = (N, M) if col_major else (M, N)
+    if out_dtype is None:
+        out_dtype = out.dtype if out is not None else torch.bfloat16
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise TypeError("out_dtype must be torch.bfloat16 or torch.float32")
     if out is None:
         if beta != 0.0:
             raise ValueError("beta != 0 needs the tensor to accumulate into (out=)")
-        out = torch.empty(shape, dtype=torch.bfloat16, device=A.device)
+        out = torch.empty(shape, dtype=out_dtype, device=A.device)
     else:
-        _require_cuda_bf16_matrix("out", out)
+        if not out.is_cuda or out.dim() != 2 or out.dtype != out_dtype:
+            raise TypeError(f"out must be a 2-D CUDA tensor of dtype {out_dtype}")
         if tuple(out.shape) != shape or out.device != A.device:
             raise ValueError(f"out must be {list(shape)} on {A.device}")
     if bias is not None:
@@ -127,8 +135,9 @@ def matmul_fused(A: torch.Tensor, B: torch.Tensor, out: Optional[torch.Tensor] =
             raise ValueError(f"bias must be a contiguous CUDA bfloat16 vector of length {N}")
     if activation not in ACTIVATIONS:
         raise ValueError(f"activation must be one of {sorted(ACTIVATIONS)}")
+    fn = lib.neogemm_bf16_nt_fused_f32 if out_dtype == torch.float32 else lib.neogemm_bf16_nt_fused
     with torch.cuda.device(A.device):
-        rc = lib.neogemm_bf16_nt_fused(
+        rc = fn(
             A.data_ptr(), B.data_ptr(), out.data_ptr(), M, N, K, _row_pitch("A", A),
             _row_pitch("B", B), _row_pitch("out", out), 1 if col_major else 0, float(alpha),
             float(beta), None if bias is None else bias.data_ptr(), ACTIVATIONS[activation], None,

@@ -81,6 +81,20 @@ int neogemm_bf16_nt_fused(const void* A, const void* B, void* C,
                           float alpha, float beta, const void* bias, int activation,
                           void* workspace, size_t workspace_bytes, void* stream);
 
+/* The fused product with an fp32 result: C holds 4-byte floats and receives
+ * act(alpha * A * B^T + beta * C + bias) unrounded (the fp32 accumulator after the epilogue
+ * arithmetic), so a caller that goes on computing in fp32 - a loss, a reduction over several
+ * products - does not pay a bf16 rounding in between.  With beta != 0 the previous fp32 contents
+ * of C are read.  ldc is in ELEMENTS (floats); C must be 4-byte aligned; the TMA-store kernels
+ * are used when ldc % 4 == 0 and C is 16-byte aligned, the direct-store kernels otherwise.
+ * Everything else as neogemm_bf16_nt_fused().  This is the other half of the intent the reference
+ * only sketches (alpha/beta parameters and an unfinished epilogue, neogemmv4.cu:166,266-267). */
+int neogemm_bf16_nt_fused_f32(const void* A, const void* B, void* C,
+                              int64_t M, int64_t N, int64_t K,
+                              int64_t lda, int64_t ldb, int64_t ldc, int c_col_major,
+                              float alpha, float beta, const void* bias, int activation,
+                              void* workspace, size_t workspace_bytes, void* stream);
+
 /* The same product for callers that must not allocate: it calls no cudaMalloc, cudaFree,
  * cudaHostAlloc or any other allocating routine, on any call.  (No counterpart in the reference.)
  *
