@@ -54,9 +54,9 @@ constexpr bool kDefaultKAlternate = false;
 constexpr int kPaceMinWaves = 8;
 constexpr int kPaceSlots = 32;
 constexpr int kPaceTimeoutNs = 20000;
-// Widest tile (columns) that has a half-size-ring kernel for two CTAs per SM (five ring stages
-// up to 32 columns, four of 24 KB at 64, three of 32 KB at 128), and the widest for which the
-// launcher picks it on its own.
+// Widest tile (columns) that has a half-size-ring kernel for two CTAs per SM (six 16 KB slots for
+// the streamed operand up to 32 columns, five at 64, four at 128; three or two for the other),
+// and the widest for which the launcher picks it on its own.
 constexpr int kResidentMaxColumns = 128;
 constexpr int kResidentAutoColumns = 128;
 // k-blocks per dynamically claimed piece of the stream-K tail pool.
@@ -101,10 +101,12 @@ const KernelEntry* kernel_table(int* count) {
       make_entry<GemmConfig<1, 16, 12, kEpiDirect>>(),
       // Half-size rings: two CTAs per SM, one whole tile each (skinny shapes with between one and
       // two tiles per SM, which then need no cut tiles and no closing reduction).
-      make_entry<GemmConfig<1, 128, 3, kEpiDirect>>(),
-      make_entry<GemmConfig<1, 64, 4, kEpiDirect>>(),
-      make_entry<GemmConfig<1, 32, 5, kEpiDirect>>(),
-      make_entry<GemmConfig<1, 16, 5, kEpiDirect>>(),
+      // Their rings are split: 4 to 6 slots for the operand streamed from DRAM, 2 or 3 for the
+      // small one every CTA re-reads from L2 (template arguments: X slots ... Y slots).
+      make_entry<GemmConfig<1, 128, 4, kEpiDirect, 1, 2>>(),
+      make_entry<GemmConfig<1, 64, 5, kEpiDirect, 1, 3>>(),
+      make_entry<GemmConfig<1, 32, 6, kEpiDirect, 1, 3>>(),
+      make_entry<GemmConfig<1, 16, 6, kEpiDirect, 1, 3>>(),
   };
   *count = static_cast<int>(sizeof(table) / sizeof(table[0]));
   return table;
@@ -154,7 +156,7 @@ bool g_encode_looked_up = false;
 
 struct Override {
   int cta_group = -1, block_n = -1, swap = -1, stream_k = -1, group_m = -1, max_ctas = -1;
-  int tuning[10] = {-1, -1, -1, -1, -1, -1, -1, -1, -1, -1};   // see neogemm_set_tuning
+  int tuning[11] = {-1, -1, -1, -1, -1, -1, -1, -1, -1, -1, -1};   // see neogemm_set_tuning
 };
 thread_local Override t_override;
 thread_local int t_last_config[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -590,7 +592,8 @@ int ensure_workspace(DeviceState* st, size_t bytes, cudaStream_t stream) {
 }
 
 int launch(DeviceState* st, const Plan& plan, const CUtensorMap& mx, const CUtensorMap& my,
-           const CUtensorMap& md, const GemmParams& params, cudaStream_t stream) {
+           const CUtensorMap& md, const GemmParams& params, cudaStream_t stream,
+           bool overlap_setup = true) {
   const KernelEntry* k = plan.kernel;
   if (!st->attr_done[plan.kernel_index]) {
     if (cudaFuncSetAttribute(k->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, k->smem_bytes) !=
@@ -606,7 +609,7 @@ int launch(DeviceState* st, const Plan& plan, const CUtensorMap& mx, const CUten
   cfg.blockDim = dim3(static_cast<unsigned>(k->threads), 1, 1);
   cfg.dynamicSmemBytes = static_cast<size_t>(k->smem_bytes);
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   int nattr = 0;
   if (k->cta_group == 2) {
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -614,6 +617,15 @@ int launch(DeviceState* st, const Plan& plan, const CUtensorMap& mx, const CUten
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     nattr = 1;
+  }
+  if (overlap_setup) {
+    // Programmatic dependent launch: this kernel's CTAs may be placed and run their set-up
+    // (barrier initialisation, tensor-memory allocation, descriptor prefetch) while the previous
+    // kernel of the stream drains; the kernel waits for that kernel's completion before its first
+    // access to global memory (griddep_wait), so ordering of data is unchanged.
+    attr[nattr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[nattr].val.programmaticStreamSerializationAllowed = 1;
+    ++nattr;
   }
   cfg.attrs = attr;
   cfg.numAttrs = nattr;
@@ -799,7 +811,7 @@ int gemm_device(const void* A, const void* B, void* C, int64_t M, int64_t N, int
   t_last_config[7] = plan.group_m;
 
   std::lock_guard<std::mutex> lock(g_mu);  // attr_done bookkeeping
-  return launch(st, plan, mx, my, md, params, stream);
+  return launch(st, plan, mx, my, md, params, stream, t_override.tuning[10] != 0);
 }
 
 int ensure_copy_queues(DeviceState* st) {
@@ -1076,7 +1088,7 @@ int neogemm_set_phase_timers(void* device_buffer, size_t bytes) {
 }
 
 int neogemm_set_tuning(int key, int value) {
-  if (key < 0 || key > 9 || (key == 6 && (value == 0 || value > 3)) || (key >= 7 && value > 1) || (key == 5 && value > 3) || value > 1000000 || (key == 0 && value > 31) || (key == 3 && value > 1) ||
+  if (key < 0 || key > 10 || (key == 6 && (value == 0 || value > 3)) || (key >= 7 && value > 1) || (key == 5 && value > 3) || value > 1000000 || (key == 0 && value > 31) || (key == 3 && value > 1) ||
       (key == 4 && value > 4))
     return NEOGEMM_ERR_BAD_ARG;
   t_override.tuning[key] = value;

@@ -218,6 +218,21 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
 }
 
 // ----------------------------------------------------------------------------------------------
+// Programmatic dependent launch.  A launch that carries the programmatic-stream-serialization
+// attribute may have its CTAs scheduled, and run their set-up, while the previous kernel of the
+// stream is still finishing; griddep_wait() then blocks until that kernel has completed and its
+// memory operations are visible.  Nothing before the wait may touch global memory.
+// griddep_launch_dependents() is the other half: it tells the scheduler that, as far as this CTA
+// is concerned, the next kernel's CTAs may be placed as soon as there is room for them.
+// ----------------------------------------------------------------------------------------------
+__device__ __forceinline__ void griddep_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void griddep_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// ----------------------------------------------------------------------------------------------
 // TMA: tiled bulk tensor copies.  Loads never use a cluster-broadcast form: every CTA fetches its
 // own box into its own shared memory.
 // ----------------------------------------------------------------------------------------------

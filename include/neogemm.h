@@ -225,6 +225,10 @@ int neogemm_set_override(int cta_group, int block_n, int swap, int stream_k, int
  *          last by one wave are asked for first by the next (fewer DRAM reads: 838 -> 752 MB at
  *          8192^3; no measurable gain in time, and the sums of those tiles then round like a
  *          reversed k loop): 1 on, 0 or -1 off.
+ *   key 10: set-up overlap.  Launches carry the programmatic-stream-serialization attribute, so
+ *          a launch's CTAs are placed and initialise barriers and tensor memory while the previous
+ *          kernel of the stream drains; the kernel still waits for that kernel's completion before
+ *          it touches global memory.  1 or -1 on, 0 off (plain stream order).
  * No counterpart in the reference (its maps only set L2 promotion, nemgemmV03.cu:52). */
 int neogemm_set_tuning(int key, int value);
 

@@ -35,7 +35,7 @@ def test_config_decode_shapes(M):
     stats, cfg = run_case(M, 28672, 8192)
     assert cfg["swap"] == 1, cfg
     # one wave of 224 whole tiles, two CTAs to an SM
-    stages = 5 if M <= 32 else (4 if M <= 64 else 3)
+    stages = 6 if M <= 32 else (5 if M <= 64 else 4)   # slots of the streamed operand
     assert (cfg["stream_k"], cfg["ctas"], cfg["stages"]) == (0, 224, stages), cfg
     stats, cfg = run_case(M, 28672, 8192, tuning={"two_ctas_per_sm": 0})   # stream-K over 148 CTAs
     assert (cfg["stream_k"], cfg["ctas"]) == (1, 148), cfg
@@ -51,7 +51,7 @@ def test_two_ctas_per_sm_whole_tiles(shape):
     # and the stream-K plan of the same shape must give the same bits where no tile is cut
     # differently - checked against the oracle, and launch to launch for determinism.
     stats, cfg = run_case(*shape, tuning={"two_ctas_per_sm": 1})
-    assert cfg["stream_k"] == 0 and cfg["ctas"] == cfg["tiles"] and cfg["stages"] in (3, 4, 5), cfg
+    assert cfg["stream_k"] == 0 and cfg["ctas"] == cfg["tiles"] and cfg["stages"] in (4, 5, 6), cfg
     run_case(*shape, tuning={"two_ctas_per_sm": 1}, col_major=True)
     A, B = make_problem(*shape, seed=5)
     dA, dB = A.cuda(), B.cuda()
