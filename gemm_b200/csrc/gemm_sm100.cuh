@@ -110,17 +110,13 @@ struct GemmParams {
 };
 
 template <int kCtaGroup_, int BLOCK_N_, int kStages_, int kEpiMode_, int kNHalves_ = 1,
-          int kStagesY_ = 0>
+          int kMHalves_ = 1>
 struct GemmConfig {
-  // kStagesY > 0: the two operands have rings of their own - kStages slots for X, kStagesY for Y.
-  // For the skinny, HBM-bound shapes X is the operand streamed once from DRAM (latency in the
-  // microseconds under load, so the deeper its ring the more bytes are in flight) and Y the small
-  // one every CTA re-reads from L2 (short latency, a shallow ring will do): splitting the rings
-  // spends the shared memory where the latency is.  These kernels also run exactly one tile per
-  // CTA (the launcher only picks them for one resident wave of whole tiles), so the epilogue's
-  // staging may live in the idle X ring instead of having shared memory of its own.
-  static constexpr int kStagesY = kStagesY_;
-  static constexpr bool kSplitRings = kStagesY_ > 0;
+  // kMHalves == 2: a CTA's tile is two 128-row blocks of X one below the other that share the Y
+  // operand, each with its own TMEM accumulator.  Made for the skinny shapes whose Y is re-read
+  // by every tile: Y enters the SM once per 256 rows of X instead of once per 128, and one CTA
+  // per SM leaves room for a deep ring.  Whole tiles only (no stream-K), direct-store epilogue.
+  static constexpr int kMHalves = kMHalves_;
   static constexpr int kCtaGroup = kCtaGroup_;
   static constexpr int BLOCK_N = BLOCK_N_;           // UMMA N
   // kNHalves == 2: the tile is two UMMA-N-wide halves side by side that share the X operand, each
@@ -132,11 +128,13 @@ struct GemmConfig {
   static constexpr int kStages = kStages_;
   static constexpr int kEpiMode = kEpiMode_;
   static constexpr int BLOCK_M = 128;                 // rows of X (TMEM lanes) per CTA
-  static constexpr int TILE_M = BLOCK_M * kCtaGroup;  // UMMA M
+  static constexpr int UMMA_M = BLOCK_M * kCtaGroup;
+  static constexpr int TILE_M = UMMA_M * kMHalves;    // rows of X per tile
   static constexpr int BLOCK_K = 64;                  // 64 bf16 = one 128-byte swizzle row
   static constexpr int UMMA_K = 16;
   static constexpr int LOAD_N = BLOCK_N / kCtaGroup;  // rows of Y each CTA fetches
-  static constexpr int SMEM_X = BLOCK_M * BLOCK_K * 2;
+  static constexpr int SMEM_X_HALF = BLOCK_M * BLOCK_K * 2;
+  static constexpr int SMEM_X = kMHalves * SMEM_X_HALF;
   static constexpr int SMEM_Y_HALF = LOAD_N * BLOCK_K * 2;
   static constexpr int SMEM_Y = kNHalves * SMEM_Y_HALF;
   static constexpr int SMEM_STAGE = SMEM_X + SMEM_Y;
@@ -153,15 +151,13 @@ struct GemmConfig {
   static constexpr int SMEM_EPI_T_WARP = kDirectCols * 64;
   static constexpr int SMEM_EPI = (kEpiMode == kEpiTmaStore) ? kEpiWarps * kEpiBufs * SMEM_EPI_WARP_BUF
                                                              : 4 * SMEM_EPI_T_WARP;
-  static constexpr int SMEM_BARRIERS = (2 * kStages + 2 * kStagesY + 8) * 8 + 16;
-  static constexpr int SMEM_RINGS = kSplitRings ? kStages * SMEM_X + kStagesY * SMEM_Y
-                                                : kStages * SMEM_STAGE;
+  static constexpr int SMEM_BARRIERS = (2 * kStages + 8) * 8 + 16;
   // +1024: the ring must start on a 1024-byte boundary for the 128-byte swizzle.
-  static constexpr int SMEM_TOTAL = SMEM_RINGS + (kSplitRings ? 0 : SMEM_EPI) + SMEM_BARRIERS + 1024;
-  static constexpr int kAccumCols = BLOCK_N;          // fp32 columns per accumulator
+  static constexpr int SMEM_TOTAL = kStages * SMEM_STAGE + SMEM_EPI + SMEM_BARRIERS + 1024;
+  static constexpr int kAccumCols = BLOCK_N * kMHalves;   // fp32 columns per accumulator set
   static constexpr int kTmemCols = (kCtaGroup == 2 || kNHalves == 2) ? 512
-      : (2 * BLOCK_N <= 32) ? 32 : (2 * BLOCK_N <= 64) ? 64 : (2 * BLOCK_N <= 128) ? 128
-      : (2 * BLOCK_N <= 256) ? 256 : 512;
+      : (2 * kAccumCols <= 32) ? 32 : (2 * kAccumCols <= 64) ? 64 : (2 * kAccumCols <= 128) ? 128
+      : (2 * kAccumCols <= 256) ? 256 : 512;
   static constexpr int kThreads = 64 + 32 * kEpiWarps;   // TMA warp, MMA warp, epilogue warps
   // A configuration that needs less than half of an SM's shared memory is built so that two of
   // its CTAs can share an SM (registers capped accordingly); both then hold a slice of tensor
@@ -177,10 +173,9 @@ struct GemmConfig {
   static_assert(kCtaGroup == 1 || kTmemCols == 512,
                 "pair mode allocates all of tensor memory so both CTAs get column 0");
   static_assert(SMEM_TOTAL <= 232448, "exceeds 227 KB of shared memory per CTA");
-  static_assert(!kSplitRings || (kCtaGroup == 1 && kNHalves == 1 && kEpiMode == kEpiDirect &&
-                                 kStagesY <= kStages && SMEM_Y % 1024 == 0 &&
-                                 SMEM_EPI <= kStages * SMEM_X),
-                "split rings: single-CTA direct-store kernels; staging borrows the X ring");
+  static_assert(kMHalves == 1 || (kMHalves == 2 && kCtaGroup == 1 && kNHalves == 1 &&
+                                  kEpiMode == kEpiDirect && 2 * kAccumCols <= 512),
+                "two M-halves: single-CTA direct-store kernels with both accumulator sets in TMEM");
   // The last tile's store epilogue borrows one 4 KB box buffer per box from the idle ring.
   static_assert(kEpiMode != kEpiTmaStore ||
                     kEpiWarps * 4 * SMEM_EPI_WARP_BUF <= kStages * SMEM_STAGE,
@@ -587,16 +582,11 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
 
   const uint32_t ring = smem_base;
-  // Split rings: X slots first, then Y slots; the staging of the (single) epilogue aliases the X
-  // ring, which is idle by then.
-  const uint32_t ring_y = ring + kStages * Cfg::SMEM_X;     // only meaningful with split rings
-  const uint32_t epi_base = Cfg::kSplitRings ? ring : ring + kStages * Cfg::SMEM_STAGE;
-  const uint32_t bar_base = Cfg::kSplitRings ? ring + Cfg::SMEM_RINGS : epi_base + Cfg::SMEM_EPI;
+  const uint32_t epi_base = ring + kStages * Cfg::SMEM_STAGE;
+  const uint32_t bar_base = epi_base + Cfg::SMEM_EPI;
   const uint32_t full_bar = bar_base;                       // [kStages]
   const uint32_t empty_bar = full_bar + 8 * kStages;        // [kStages]
-  const uint32_t full_y_bar = empty_bar + 8 * kStages;      // [kStagesY]
-  const uint32_t empty_y_bar = full_y_bar + 8 * Cfg::kStagesY;   // [kStagesY]
-  const uint32_t tmem_full_bar = empty_y_bar + 8 * Cfg::kStagesY;   // [2]
+  const uint32_t tmem_full_bar = empty_bar + 8 * kStages;   // [2]
   const uint32_t tmem_empty_bar = tmem_full_bar + 16;       // [2]
   const uint32_t sched_full_bar = tmem_empty_bar + 16;      // [2] dynamic-claim queue
   const uint32_t sched_empty_bar = sched_full_bar + 16;     // [2]
@@ -622,10 +612,6 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
     for (int s = 0; s < kStages; ++s) {
       mbar_init(full_bar + 8 * s, 1);   // one arrive.expect_tx per phase (leader's producer)
       mbar_init(empty_bar + 8 * s, 1);  // one tcgen05.commit per phase
-    }
-    for (int s = 0; s < Cfg::kStagesY; ++s) {
-      mbar_init(full_y_bar + 8 * s, 1);
-      mbar_init(empty_y_bar + 8 * s, 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tmem_full_bar + 8 * a, 1);               // one tcgen05.commit per tile
@@ -693,67 +679,6 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
         // the sum of a tile's k-blocks does not care which came first (the order is fixed per
         // tile, so results stay reproducible).
         const bool reverse_k = p.k_alternate != 0 && (seg_idx & 1) != 0 && seg.n_contrib == 1;
-        if constexpr (Cfg::kSplitRings) {
-          // One tile per CTA: a second segment would find the epilogue's staging in the X ring.
-          if (seg_idx > 0) {
-            if (lane == 0) report_error(p, abort_flag, kDevBounds, seg_idx, 4);
-            ok = false;
-            break;
-          }
-          // X runs kSkew k-blocks ahead of Y.  Slot of X(k) frees when MMA(k - kStages) is done,
-          // slot of Y(k) when MMA(k - kStagesY) is done: issuing X(i) and Y(i - kSkew) in the same
-          // turn makes both wait for the same MMA, so one in-order loop serves both rings.
-          constexpr int kSkew = kStages - Cfg::kStagesY;
-          uint32_t stage_y = 0, phase_y = 0;
-          for (int i = 0; i < seg.kb_count + kSkew && ok; ++i) {
-            if (i < seg.kb_count) {
-              wait_timer.begin();
-              const bool got = __all_sync(0xffffffffu,
-                                          mbar_wait(empty_bar + 8 * stage, phase ^ 1, abort_flag,
-                                                    static_cast<uint32_t>(p.main_wait_hint_ns)));
-              wait_timer.end();
-              if (!got) {
-                if (lane == 0)
-                  report_error(p, abort_flag, kDevTimeoutProducer, seg_idx, static_cast<int>(stage));
-                ok = false;
-                break;
-              }
-              if (elect_one()) {
-                const int kb = seg.kb_begin + i;
-                const int c0 = (reverse_k ? (seg.kb_begin + kb_end - 1 - kb) : kb) * Cfg::BLOCK_K;
-                const uint32_t sx = ring + stage * Cfg::SMEM_X;
-                mbar_arrive_expect_tx(full_bar + 8 * stage, Cfg::SMEM_X);
-                if (hint_x) tma_load_2d_hint(sx, &tmap_x, full_bar + 8 * stage, c0, row_x, pol_x);
-                else tma_load_2d(sx, &tmap_x, full_bar + 8 * stage, c0, row_x);
-              }
-              __syncwarp();
-              if (++stage == kStages) { stage = 0; phase ^= 1; }
-            }
-            if (i >= kSkew) {
-              const bool got = __all_sync(0xffffffffu,
-                                          mbar_wait(empty_y_bar + 8 * stage_y, phase_y ^ 1, abort_flag,
-                                                    static_cast<uint32_t>(p.main_wait_hint_ns)));
-              if (!got) {
-                if (lane == 0)
-                  report_error(p, abort_flag, kDevTimeoutProducer, seg_idx, 100 + static_cast<int>(stage_y));
-                ok = false;
-                break;
-              }
-              if (elect_one()) {
-                const int kb = seg.kb_begin + i - kSkew;
-                const int c0 = (reverse_k ? (seg.kb_begin + kb_end - 1 - kb) : kb) * Cfg::BLOCK_K;
-                const uint32_t sy = ring_y + stage_y * Cfg::SMEM_Y;
-                mbar_arrive_expect_tx(full_y_bar + 8 * stage_y, Cfg::SMEM_Y);
-                if (hint_y) tma_load_2d_hint(sy, &tmap_y, full_y_bar + 8 * stage_y, c0, row_y, pol_y);
-                else tma_load_2d(sy, &tmap_y, full_y_bar + 8 * stage_y, c0, row_y);
-              }
-              __syncwarp();
-              if (++stage_y == Cfg::kStagesY) { stage_y = 0; phase_y ^= 1; }
-            }
-          }
-          ++seg_idx;
-          continue;
-        }
         for (int kb = seg.kb_begin; kb < kb_end; ++kb) {
           wait_timer.begin();
           const bool got = __all_sync(0xffffffffu,
@@ -813,9 +738,8 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
                     abort_flag);
       Segment seg;
       uint32_t stage = 0, phase = 0;
-      uint32_t stage_y = 0, phase_y = 0;   // split rings only
       int seg_idx = 0;
-      constexpr uint32_t idesc = make_idesc_bf16(Cfg::TILE_M, BLOCK_N);
+      constexpr uint32_t idesc = make_idesc_bf16(Cfg::UMMA_M, BLOCK_N);
       bool ok = true;
       GemmParams timer_params = p;
       if (lane != 0) timer_params.timers = nullptr;
@@ -925,42 +849,34 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
             ok = false;
             break;
           }
-          if constexpr (Cfg::kSplitRings) {
-            const bool got_y = __all_sync(0xffffffffu,
-                                          mbar_wait(full_y_bar + 8 * stage_y, phase_y, abort_flag,
-                                                    static_cast<uint32_t>(p.main_wait_hint_ns)));
-            if (!got_y) {
-              if (lane == 0)
-                report_error(p, abort_flag, kDevTimeoutMmaFull, seg_idx, 100 + static_cast<int>(stage_y));
-              ok = false;
-              break;
-            }
-          }
           tcgen05_fence_after();
-          const uint32_t sx = Cfg::kSplitRings ? ring + stage * Cfg::SMEM_X
-                                               : ring + stage * Cfg::SMEM_STAGE;
+          const uint32_t sx = ring + stage * Cfg::SMEM_STAGE;
           const uint64_t desc_x = make_smem_desc_sw128(sx);
-          const uint64_t desc_y = make_smem_desc_sw128(
-              Cfg::kSplitRings ? ring_y + stage_y * Cfg::SMEM_Y : sx + Cfg::SMEM_X);
+          const uint64_t desc_y = make_smem_desc_sw128(sx + Cfg::SMEM_X);
           if (elect_one()) {
 #pragma unroll
             for (int k = 0; k < Cfg::BLOCK_K / Cfg::UMMA_K; ++k) {
               // +32 bytes (two 16-byte units) per 16-element K step inside the swizzle row.
+              if constexpr (Cfg::kMHalves == 2) {
+                // Two blocks of X rows, one Y: the second block sits SMEM_X_HALF further on.
 #pragma unroll
-              for (int h = 0; h < Cfg::kNHalves; ++h)
-                umma_bf16<kCtaGroup>(tmem_d + h * Cfg::kAccumCols, desc_x + 2 * k,
-                                     desc_y + h * kHalfStep + 2 * k, idesc,
-                                     (kb > 0 || k > 0) ? 1u : 0u);
+                for (int mh = 0; mh < 2; ++mh)
+                  umma_bf16<kCtaGroup>(tmem_d + mh * BLOCK_N,
+                                       desc_x + mh * (Cfg::SMEM_X_HALF >> 4) + 2 * k, desc_y + 2 * k,
+                                       idesc, (kb > 0 || k > 0) ? 1u : 0u);
+              } else {
+#pragma unroll
+                for (int h = 0; h < Cfg::kNHalves; ++h)
+                  umma_bf16<kCtaGroup>(tmem_d + h * Cfg::kAccumCols, desc_x + 2 * k,
+                                       desc_y + h * kHalfStep + 2 * k, idesc,
+                                       (kb > 0 || k > 0) ? 1u : 0u);
+              }
             }
             if (kCtaGroup == 2) umma_commit_both_ctas(empty_bar + 8 * stage);
             else umma_commit<1>(empty_bar + 8 * stage);
-            if (Cfg::kSplitRings) umma_commit<1>(empty_y_bar + 8 * stage_y);
           }
           __syncwarp();
           if (++stage == kStages) { stage = 0; phase ^= 1; }
-          if (Cfg::kSplitRings) {
-            if (++stage_y == static_cast<uint32_t>(Cfg::kStagesY)) { stage_y = 0; phase_y ^= 1; }
-          }
         }
         if (!ok) break;
         if (elect_one()) {
@@ -1001,7 +917,6 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
     PhaseTimer wait_timer(timer_params), loop_timer(timer_params);
     loop_timer.begin();
     while (ok && it.next(seg, lane)) {
-      if (Cfg::kSplitRings && seg_idx > 0) break;   // one tile per CTA (the producer reports it)
       const uint32_t acc = (Cfg::kNHalves == 1) ? (seg_idx & 1) : 0;
       const uint32_t acc_phase = (Cfg::kNHalves == 1) ? ((seg_idx >> 1) & 1) : (seg_idx & 1);
       // Is this the CTA's last segment?  Then, once its accumulator is complete, nothing reads
@@ -1021,12 +936,14 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
       // read its share, and the index arithmetic alone was ~1500 cycles of that.
       int tm, tn;
       tile_coords(p, seg.tile, tm, tn);
-      const int row0 = tm * Cfg::TILE_M + static_cast<int>(cta_rank) * Cfg::BLOCK_M;
+      const int row0_tile = tm * Cfg::TILE_M + static_cast<int>(cta_rank) * Cfg::BLOCK_M;
       const int col0 = tn * Cfg::TILE_N;
-      const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + acc * Cfg::kAccumCols;
+      const uint32_t taddr_tile = tmem_base + ((quad * 32u) << 16) + acc * Cfg::kAccumCols;
+      const int row0 = row0_tile;            // (the direct-store walk shadows these per M-half)
+      const uint32_t taddr = taddr_tile;
       // Pin the values in registers here; otherwise the compiler sinks the arithmetic to its first
       // use, which is behind the wait.
-      asm volatile("" ::"r"(row0), "r"(col0), "r"(taddr));
+      asm volatile("" ::"r"(row0_tile), "r"(col0), "r"(taddr_tile));
       wait_timer.begin();
       // One lane polls; the other 31 sleep at the shuffle instead of hammering the barrier.
       int got_i = 0;
@@ -1052,7 +969,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
       // ---- stream-K: publish this segment's partial; the last arriver finishes the rows ----
       bool finish = true;
       const float* tile_partials = nullptr;
-      if constexpr (Cfg::kNHalves == 1) {
+      if constexpr (Cfg::kNHalves == 1 && Cfg::kMHalves == 1) {
         if (seg.n_contrib > 1) {
           // Slot layout [contributor][column][row] so that a warp's 32 rows of one column are
           // one 128-byte line.  Counters are per (tile, CTA of the pair, lane quadrant): the
@@ -1356,6 +1273,11 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
           ++store_count;
         }
       } else {
+        // Two M-halves: the same walk twice, 128 rows and BLOCK_N accumulator columns further on.
+#pragma unroll 1
+        for (int mh = 0; mh < Cfg::kMHalves; ++mh) {
+        const int row0 = row0_tile + mh * Cfg::BLOCK_M;
+        const uint32_t taddr = taddr_tile + static_cast<uint32_t>(mh) * BLOCK_N;
         const int row = row0 + row_in_cta;
         __nv_bfloat16* out_row = p.out + static_cast<long long>(row) * p.out_stride_r;
         const bool vec_ok = (p.out_stride_c == 1) && ((p.out_stride_r & 7) == 0) &&
@@ -1467,6 +1389,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
               }
             }
           }
+        }
         }
       }
 

@@ -50,15 +50,18 @@ constexpr double kEpilogueUs = 3.0;
 // More than kPaceSlots paced launches in flight at once wrap around and share counters: results
 // are unaffected (the wait is soft, nothing depends on it) but a worker that reads a foreign count
 // may idle up to the time-out at a wave's start.
-constexpr bool kDefaultKAlternate = false;
+// Whole tiles of odd waves walk K backwards (plain round-robin schedules of the TMA-store kernels
+// with more than one wave): together with raster groups of 16 tile rows it took 8192^3 from
+// 689.3 to 684.2 us in 20-launch bursts and from 761.6 to 757.8 us under seconds of load (cuBLAS
+// 690.2 / 763.3 on the same GPU), by way of fewer DRAM reads under the power cap.
+constexpr bool kDefaultKAlternate = true;
 constexpr int kPaceMinWaves = 8;
 constexpr int kPaceSlots = 32;
 constexpr int kPaceTimeoutNs = 20000;
-// Widest tile (columns) that has a half-size-ring kernel for two CTAs per SM (six 16 KB slots for
-// the streamed operand up to 32 columns, five at 64, four at 128; three or two for the other),
-// and the widest for which the launcher picks it on its own.
+// Widest tile (columns) that has a half-size-ring kernel for two CTAs per SM (five ring stages
+// up to 32 columns, four of 24 KB at 64, three of 32 KB at 128) or a tall-tile kernel.
 constexpr int kResidentMaxColumns = 128;
-constexpr int kResidentAutoColumns = 128;
+
 // k-blocks per dynamically claimed piece of the stream-K tail pool.
 constexpr int kDynPieceKBlocks = 16;
 // Row chunks the host entry point cuts the uploaded operand into (one product launch each).
@@ -71,6 +74,7 @@ constexpr int kDefaultDynPieces = 1;
 // ------------------------------------------------------------------------------------------
 struct KernelEntry {
   int cta_group, block_n, stages, epi, halves;
+  int mhalves;  // 128-row blocks of X per CTA tile (2: tall tile sharing Y)
   int per_sm;   // CTAs of this kernel that fit on one SM together (1 or 2)
   const void* fn;
   int smem_bytes;
@@ -81,7 +85,7 @@ struct KernelEntry {
 template <class Cfg>
 KernelEntry make_entry() {
   return KernelEntry{Cfg::kCtaGroup, Cfg::BLOCK_N, Cfg::kStages, Cfg::kEpiMode, Cfg::kNHalves,
-                     Cfg::kCtasPerSm, reinterpret_cast<const void*>(&gemm_bf16_nt_kernel<Cfg>), Cfg::SMEM_TOTAL,
+                     Cfg::kMHalves, Cfg::kCtasPerSm, reinterpret_cast<const void*>(&gemm_bf16_nt_kernel<Cfg>), Cfg::SMEM_TOTAL,
                      Cfg::kTmemCols, Cfg::kThreads};
 }
 
@@ -101,24 +105,29 @@ const KernelEntry* kernel_table(int* count) {
       make_entry<GemmConfig<1, 16, 12, kEpiDirect>>(),
       // Half-size rings: two CTAs per SM, one whole tile each (skinny shapes with between one and
       // two tiles per SM, which then need no cut tiles and no closing reduction).
-      // Their rings are split: 4 to 6 slots for the operand streamed from DRAM, 2 or 3 for the
-      // small one every CTA re-reads from L2 (template arguments: X slots ... Y slots).
+      make_entry<GemmConfig<1, 128, 3, kEpiDirect>>(),
+      make_entry<GemmConfig<1, 64, 4, kEpiDirect>>(),
+      make_entry<GemmConfig<1, 32, 5, kEpiDirect>>(),
+      make_entry<GemmConfig<1, 16, 5, kEpiDirect>>(),
+      // Tall tiles: 256 rows of X per CTA (two 128-row blocks sharing Y), one CTA per SM, ring
+      // filled to 227 KB.  Same use as the four above - one resident wave of whole tiles - with
+      // Y entering the SM once per 256 rows and more bytes of the streamed operand in flight.
       make_entry<GemmConfig<1, 128, 4, kEpiDirect, 1, 2>>(),
-      make_entry<GemmConfig<1, 64, 5, kEpiDirect, 1, 3>>(),
-      make_entry<GemmConfig<1, 32, 6, kEpiDirect, 1, 3>>(),
-      make_entry<GemmConfig<1, 16, 6, kEpiDirect, 1, 3>>(),
+      make_entry<GemmConfig<1, 64, 5, kEpiDirect, 1, 2>>(),
+      make_entry<GemmConfig<1, 32, 6, kEpiDirect, 1, 2>>(),
+      make_entry<GemmConfig<1, 16, 6, kEpiDirect, 1, 2>>(),
   };
   *count = static_cast<int>(sizeof(table) / sizeof(table[0]));
   return table;
 }
 
 const KernelEntry* find_kernel(int cta_group, int block_n, int epi, int halves, int per_sm,
-                               int* index) {
+                               int mhalves, int* index) {
   int n;
   const KernelEntry* t = kernel_table(&n);
   for (int i = 0; i < n; ++i) {
     if (t[i].cta_group == cta_group && t[i].block_n == block_n && t[i].epi == epi &&
-        t[i].halves == halves && t[i].per_sm == per_sm) {
+        t[i].halves == halves && t[i].per_sm == per_sm && t[i].mhalves == mhalves) {
       if (index) *index = i;
       return &t[i];
     }
@@ -143,7 +152,7 @@ struct DeviceState {
   std::mutex host_entry_mu;    // one neogemm_bf16_nt_host call at a time per device
   void* stage[3] = {nullptr, nullptr, nullptr};  // device copies of A, B, C for the host entry
   size_t stage_bytes[3] = {0, 0, 0};
-  bool attr_done[16] = {};
+  bool attr_done[32] = {};
   // Host entry point: copy queues for the two PCIe directions and the events that order them.
   cudaStream_t copy_in = nullptr, copy_out = nullptr;
   cudaEvent_t copy_events[2 * 16 + 1] = {};
@@ -293,6 +302,7 @@ struct Plan {
   int cta_group = 1, block_n = 256, epi = kEpiTmaStore;
   int halves = 1;           // 2: 256 x 512 pair tile (two UMMA-N halves sharing X)
   int per_sm = 1;           // 2: half-size rings, two CTAs per SM, one whole tile each
+  int mhalves = 1;          // 2: tall tiles, 256 rows of X per CTA sharing Y, one whole tile each
   bool stream_k = false;
   int sk_first_tile = 0;    // tiles below are handed out round-robin, tiles from here on are cut
   int sk_splits = 0;        // > 0: uniform k-chunks per cut tile (large kernels)
@@ -422,38 +432,57 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
   p.block_n = block_n;
   p.cta_group = cta_group;
   p.epi = epi;
-  const int tile_m = 128 * cta_group;
+  // Skinny shapes with more 128-row tiles than SMs but at most two per SM (decode: 224 on 148)
+  // run as ONE wave of whole tiles: every CTA streams its rows of X over all of K, nothing is
+  // cut, nothing has to be summed at the end.  Two kernels can do that.  Tall tiles (the default):
+  // 256 rows of X per CTA, one CTA per SM - cuBLAS' choice for M=16 has the same shape
+  // (nvjet_tst_256x16: 112 whole tiles of 256 rows).  The small operand enters an SM once per 256
+  // rows instead of once per 128 (at M=128 it is as large as the streamed one: 8 MB -> 6 MB into
+  // the SMs that carried two tiles), and a ring that fills the SM.  Or 128-row tiles with two
+  // CTAs per SM and half-size rings.  Tuning key 7: -1 tall tiles when they fit in one wave,
+  // 0 neither (stream-K), 1 two CTAs per SM, 2 tall tiles even where 128-row tiles would fit.
+  int mhalves = 1;
+  {
+    const int64_t tiles128 = ((md + 127) / 128) * ((nd + block_n - 1) / block_n);
+    const int64_t tiles256 = ((md + 255) / 256) * ((nd + block_n - 1) / block_n);
+    const bool eligible = epi == kEpiDirect && cta_group == 1 && block_n <= kResidentMaxColumns &&
+                          ov.stream_k <= 0 && ov.max_ctas <= 0 && (K + 63) / 64 >= 16 &&
+                          tiles256 <= sm_count;
+    if (eligible && ((ov.tuning[7] < 0 && tiles128 > sm_count && tiles128 <= 2ll * sm_count) ||
+                     ov.tuning[7] == 2))
+      mhalves = 2;
+  }
+  p.mhalves = mhalves;
+  const int tile_m = 128 * cta_group * mhalves;
   p.num_m_tiles = static_cast<int>((md + tile_m - 1) / tile_m);
   const int tile_n = block_n * p.halves;
   p.num_n_tiles = static_cast<int>((nd + tile_n - 1) / tile_n);
   const int64_t tiles = static_cast<int64_t>(p.num_m_tiles) * p.num_n_tiles;
   if (tiles > 0x3fffffffll) return NEOGEMM_ERR_UNSUPPORTED;
 
-  // Skinny shapes with more tiles than SMs but at most two per SM (decode: 224 tiles of 128 rows
-  // on 148 SMs) run as ONE wave of whole tiles, two CTAs per SM with half-size rings: every CTA
-  // streams one tile's rows over all of K, nothing is cut, nothing has to be summed at the end.
-  // cuBLAS' choice for M=16 has the same shape (112 whole tiles of 256 rows, no split-K).
-  // Measured (CUDA-graph replays, M x 28672 x 8192): M=16 78.3 -> 74.2 us, M=32 81.8 -> 76.9 us,
-  // M=64 84.4 -> 83.0 us (K=4096: 48.2 -> 40.2 us), M=128 87.8 -> 82.8 us, M=96 91.6 -> 84.3 us.
-  // Tuning key 7: -1 auto, 0 never, 1 whenever the kernel exists and the tiles fit.
+  // The other one-wave plan for skinny shapes (see above): 128-row tiles, two CTAs per SM with
+  // half-size rings.  Measured before tall tiles existed (CUDA-graph replays, M x 28672 x 8192,
+  // against stream-K on 148 CTAs): M=16 78.3 -> 74.2 us, M=32 81.8 -> 76.9 us, M=64 84.4 -> 83.0 us
+  // (K=4096: 48.2 -> 40.2 us), M=128 87.8 -> 82.8 us, M=96 91.6 -> 84.3 us.  Picked only on
+  // request (tuning key 7 = 1), whenever the kernel exists and all tiles fit at once.
   int per_sm = 1;
-  if (epi == kEpiDirect && cta_group == 1 && ov.tuning[7] != 0 && ov.stream_k <= 0 &&
-      ov.max_ctas <= 0 && tiles <= 2ll * sm_count && (K + 63) / 64 >= 16) {
-    const bool forced = (ov.tuning[7] == 1) && block_n <= kResidentMaxColumns;
-    const bool automatic = (ov.tuning[7] < 0) && block_n <= kResidentAutoColumns && tiles > sm_count;
-    if (forced || automatic) per_sm = 2;
-  }
+  if (epi == kEpiDirect && cta_group == 1 && mhalves == 1 && ov.tuning[7] == 1 && ov.stream_k <= 0 &&
+      ov.max_ctas <= 0 && tiles <= 2ll * sm_count && (K + 63) / 64 >= 16 &&
+      block_n <= kResidentMaxColumns)
+    per_sm = 2;
   p.per_sm = per_sm;
-  p.kernel = find_kernel(cta_group, block_n, epi, p.halves, per_sm, &p.kernel_index);
+  p.kernel = find_kernel(cta_group, block_n, epi, p.halves, per_sm, mhalves, &p.kernel_index);
   if (p.kernel == nullptr) return NEOGEMM_ERR_UNSUPPORTED;
 
   p.num_tiles = static_cast<int>(tiles);
   p.num_k_blocks = static_cast<int>((K + 63) / 64);
 
   // Raster group height (tile rows walked before moving one tile column on).  Pair tiles: 8 rows
-  // (2048 rows of X) keep a wave near square; tall problems re-read all of Y once per group, so
-  // they take 16 (measured at 65536 x 8192 x 8192: +5 %).
-  p.group_m = (cta_group == 2) ? ((p.num_m_tiles >= 64) ? 16 : 8) : 16;
+  // (2048 rows of X) keep a wave near square; from 8192 rows on the groups are 16 tall: tall
+  // problems re-read all of Y once per group (measured at 65536 x 8192 x 8192: +5 %), and with
+  // the K direction alternating between waves 16 is the best height at 8192^3 too (12: 685.4 us,
+  // 16: 684.2, 20: 686.3, 24: 691.2).
+  p.group_m = (cta_group == 2) ? ((p.num_m_tiles >= 32) ? 16 : 8) : 16;
   if (ov.group_m > 0) p.group_m = ov.group_m;
   p.group_m = std::max(1, std::min(p.group_m, p.num_m_tiles));
 
@@ -469,7 +498,7 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
   //    4096^3 is 3.46 waves of pair tiles).
   bool stream_k = false;
   int sk_first = 0, sk_splits = 0;
-  if (per_sm == 2) {
+  if (per_sm == 2 || mhalves == 2) {
     // one whole tile per CTA, all resident at once
   } else if (epi == kEpiDirect) {
     if (p.num_tiles < workers) {
@@ -696,7 +725,7 @@ int gemm_device(const void* A, const void* B, void* C, int64_t M, int64_t N, int
   const int promo = (t_override.tuning[5] >= 0 && t_override.tuning[5] < 3)
       ? -1 - t_override.tuning[5] : 0;
   rc = get_tensor_map(X, static_cast<uint64_t>(K), static_cast<uint64_t>(plan.Md),
-                      static_cast<uint64_t>(ldx) * 2, 128, promo, &mx);
+                      static_cast<uint64_t>(ldx) * 2, 128u * plan.mhalves, promo, &mx);
   if (rc != NEOGEMM_OK) return rc;
   rc = get_tensor_map(Y, static_cast<uint64_t>(K), static_cast<uint64_t>(plan.Nd),
                       static_cast<uint64_t>(ldy) * 2,
@@ -1088,7 +1117,7 @@ int neogemm_set_phase_timers(void* device_buffer, size_t bytes) {
 }
 
 int neogemm_set_tuning(int key, int value) {
-  if (key < 0 || key > 10 || (key == 6 && (value == 0 || value > 3)) || (key >= 7 && value > 1) || (key == 5 && value > 3) || value > 1000000 || (key == 0 && value > 31) || (key == 3 && value > 1) ||
+  if (key < 0 || key > 10 || (key == 6 && (value == 0 || value > 3)) || (key >= 8 && value > 1) || (key == 7 && value > 2) || (key == 5 && value > 3) || value > 1000000 || (key == 0 && value > 31) || (key == 3 && value > 1) ||
       (key == 4 && value > 4))
     return NEOGEMM_ERR_BAD_ARG;
   t_override.tuning[key] = value;
@@ -1432,7 +1461,7 @@ int neogemm_bf16_nt_noalloc(const void* A, const void* B, void* C, int64_t M, in
   CUtensorMap mx, my, md;
   std::memset(&md, 0, sizeof(md));
   rc = encode_map_uncached(X, static_cast<uint64_t>(K), static_cast<uint64_t>(plan.Md),
-                           static_cast<uint64_t>(ldx) * 2, 128, 0, &mx);
+                           static_cast<uint64_t>(ldx) * 2, 128u * plan.mhalves, 0, &mx);
   if (rc != NEOGEMM_OK) return rc;
   rc = encode_map_uncached(Y, static_cast<uint64_t>(K), static_cast<uint64_t>(plan.Nd),
                            static_cast<uint64_t>(ldy) * 2,
@@ -1472,6 +1501,9 @@ int neogemm_bf16_nt_noalloc(const void* A, const void* B, void* C, int64_t M, in
   params.max_contrib = plan.max_contrib;
   params.status = st->status;
   params.timers = nullptr;
+  // Same K-direction rule as the regular entry point, so that both give the same bits.
+  params.k_alternate = (kDefaultKAlternate && !plan.stream_k && plan.epi == kEpiTmaStore &&
+                        plan.num_tiles > plan.num_ctas / plan.cta_group) ? 1 : 0;
   if (plan.stream_k) {
     // Every call shares the array and it keeps the previous call's contents: the arrival
     // counters must start at zero, so clear their region in stream order before the launch.

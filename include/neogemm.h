@@ -215,16 +215,21 @@ int neogemm_set_override(int cta_group, int block_n, int swap, int stream_k, int
  *          be claimed at run time instead of assigning them statically (0 = none, up to 4).
  *   key 6: two-half tiles: k-blocks (1..3) issued for the first half alone at the start of a tile,
  *          while the epilogue still reads the second half of the previous tile.
- *   key 7: skinny shapes with between one and two tiles per SM as ONE wave of whole tiles, two
- *          CTAs per SM with half-size rings (no cut tiles, no closing sums): -1 chosen by the
- *          launcher, 0 never, 1 whenever such a kernel exists and all tiles fit at once.
+ *   key 7: skinny shapes that need between one and two 128-row tiles per SM run as ONE wave of
+ *          whole tiles (no cut tiles, no closing sums): -1 with tall tiles (256 rows per CTA
+ *          sharing the small operand, one CTA per SM), 0 not at all (stream-K instead),
+ *          1 with 128-row tiles, two CTAs per SM and half-size rings, whenever such a kernel
+ *          exists and all tiles fit at once, 2 with tall tiles whenever they fit in one wave.
  *   key 8: wave pacing of launches with many waves of whole tiles (workers wait, briefly and
  *          without obligation, for each other at the start of every wave so that tiles sharing
  *          operand panels keep sharing them in L2): -1 from 8 waves on, 0 off, 1 from 2 waves on.
  *   key 9: whole tiles of odd waves walk K backwards, so that the k-slices of a row panel used
  *          last by one wave are asked for first by the next (fewer DRAM reads: 838 -> 752 MB at
- *          8192^3; no measurable gain in time, and the sums of those tiles then round like a
- *          reversed k loop): 1 on, 0 or -1 off.
+ *          8192^3, which under the power cap is worth 0.5-0.8 % of time; the sums of those tiles
+ *          then round like a reversed k loop - results stay reproducible launch to launch, the
+ *          order is a fixed property of the tile's place in the schedule): -1 on for plain
+ *          round-robin schedules of the TMA-store kernels with more than one wave, 0 off, 1 on
+ *          for every schedule.
  *   key 10: set-up overlap.  Launches carry the programmatic-stream-serialization attribute, so
  *          a launch's CTAs are placed and initialise barriers and tensor memory while the previous
  *          kernel of the stream drains; the kernel still waits for that kernel's completion before

@@ -75,22 +75,30 @@ def test_data_parallel_and_mixed_plans_cover_the_problem(shape, col_major):
 
 @pytest.mark.parametrize("M", [8, 16, 32, 64, 128])
 def test_decode_shapes_run_as_one_wave_of_whole_tiles(M):
-    # 224 tiles on 148 SMs: two CTAs per SM with half-size rings, one whole tile each.
+    # 28672 rows of B on 148 SMs: 112 tall tiles (256 rows each, one CTA per SM), one whole tile
+    # per CTA, nothing cut.
     p, segs = plan(M, 28672, 8192)
-    stages = 6 if M <= 32 else (5 if M <= 64 else 4)   # slots of the streamed operand
+    stages = 6 if M <= 32 else (5 if M <= 64 else 4)
     assert (p["swap"], p["stream_k"], p["cta_group"], p["stages"]) == (1, 0, 1, stages)
-    assert p["tiles"] == 224 and p["ctas"] == 224 and p["max_contrib"] == 0
+    assert p["tiles"] == 112 and p["ctas"] == 112 and p["max_contrib"] == 0
     check_cover(p, segs)
-    assert sorted(s[0] for s in segs) == list(range(224)) and all(s[3] == 128 for s in segs)
-    # not when the tiles fit one per SM, when there are more than two per SM, or for short K
+    assert sorted(s[0] for s in segs) == list(range(112)) and all(s[3] == 128 for s in segs)
+    # not when 128-row tiles fit one per SM, when there are more than two per SM, or for short K
     assert plan(M, 148 * 128, 8192)[0]["ctas"] == 148
     assert plan(M, 297 * 128, 8192)[0]["ctas"] == 148
     assert plan(M, 28672, 512)[0]["ctas"] == 148
-    # forced on (also below one tile per SM) and off
-    assert plan(M, 100 * 128, 8192, tuning={7: 1})[0]["stages"] == stages
+    # forced on (also below one 128-row tile per SM) and off
+    p2, _ = plan(M, 100 * 128, 8192, tuning={7: 2})
+    assert (p2["tiles"], p2["ctas"], p2["stages"]) == (50, 50, stages)
     p, segs = plan(M, 28672, 8192, tuning={7: 0})
     assert (p["stream_k"], p["ctas"]) == (1, 148)
     check_cover(p, segs)
+    # the other one-wave plan: 224 tiles of 128 rows, two CTAs per SM with half-size rings
+    p, segs = plan(M, 28672, 8192, tuning={7: 1})
+    half_stages = 5 if M <= 32 else (4 if M <= 64 else 3)
+    assert (p["stream_k"], p["tiles"], p["ctas"], p["stages"]) == (0, 224, 224, half_stages)
+    check_cover(p, segs)
+    assert plan(M, 100 * 128, 8192, tuning={7: 1})[0]["stages"] == half_stages
 
 
 @pytest.mark.parametrize("M", [16, 64, 128])

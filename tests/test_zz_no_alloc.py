@@ -73,7 +73,7 @@ def test_noalloc_with_scratch_matches_regular_entry_point_twice(shape):
     _check_twice(shape, uses_scratch=True)
 
 
-# Plans that need no scratch: one wave of whole tiles with two CTAs per SM (the decode shapes)
+# Plans that need no scratch: one wave of whole tall tiles (the decode shapes)
 # and a data-parallel TMA-store plan.
 @pytest.mark.parametrize("shape", [(16, 28672, 8192), (128, 28672, 8192), (1024, 768, 512)])
 def test_noalloc_without_scratch_matches_regular_entry_point_twice(shape):
