@@ -119,9 +119,17 @@ def test_fp32_result_plain_and_fused(shape):
     assert ops.device_status()[0] == 0
     stats = assert_fp32_result(out, ref, f"fp32 result {shape} cfg={cfg}")
     assert cfg["block_n"] <= 256, cfg   # never the two-half tile
-    # the same product rounded once must be the bf16 entry point's result, bit for bit
-    assert torch.equal(out.to(torch.bfloat16).view(torch.int16),
-                       ops.matmul(dA, dB).view(torch.int16)), (shape, cfg, stats)
+    # The same product rounded once must be the bf16 entry point's result, bit for bit - with K
+    # walked forwards by every tile in both: the bf16 entry point may pick a different tile (and
+    # so different waves), and by default the K direction alternates from wave to wave.
+    ops.set_tuning("k_direction_alternates", 0)
+    try:
+        fwd32 = ops.matmul_fused(dA, dB, out_dtype=torch.float32)
+        fwd16 = ops.matmul(dA, dB)
+    finally:
+        ops.set_tuning("k_direction_alternates", -1)
+    assert torch.equal(fwd32.to(torch.bfloat16).view(torch.int16), fwd16.view(torch.int16)), \
+        (shape, cfg, stats)
     # alpha, beta (read as fp32), bias and activation on top
     g = torch.Generator().manual_seed(5)
     c_old = torch.randn(M, N, generator=g) * 0.05

@@ -3,7 +3,7 @@ import pytest
 import torch
 
 from gemm_b200 import ops
-from tests.util import run_case
+from tests.util import gpu_bits_compare, run_case
 
 pytestmark = pytest.mark.gpu
 
@@ -97,6 +97,9 @@ def test_wide_pair_tile_is_deterministic_and_never_wide_when_switched_off():
     A, B = make_problem(2048, 4096, 1024, seed=14)
     dA, dB = A.cuda(), B.cuda()
     ops.set_tuning("wide_tile", 1)
+    # K walked forwards by every tile (the default alternates the direction from wave to wave,
+    # and the two kernels have different waves), so that both sum every element in the same order.
+    ops.set_tuning("k_direction_alternates", 0)
     try:
         first = ops.matmul(dA, dB).clone()
         assert ops.last_config()["block_n"] == 512
@@ -105,12 +108,20 @@ def test_wide_pair_tile_is_deterministic_and_never_wide_when_switched_off():
         ops.set_tuning("wide_tile", 0)
         other = ops.matmul(dA, dB)
         assert ops.last_config()["block_n"] <= 256
+        # with the default direction rule the narrower kernel (two waves) still repeats itself
+        ops.set_tuning("k_direction_alternates", -1)
+        again = ops.matmul(dA, dB).clone()
+        for _ in range(4):
+            assert torch.equal(again.view(torch.int16), ops.matmul(dA, dB).view(torch.int16))
     finally:
         ops.set_tuning("wide_tile", -1)
+        ops.set_tuning("k_direction_alternates", -1)
     torch.cuda.synchronize()
     assert ops.device_status()[0] == 0
     # same k order per element in both kernels -> identical bits
     assert torch.equal(first.view(torch.int16), other.view(torch.int16))
+    s = gpu_bits_compare(again, first)
+    assert s["max_ulp"] <= 1 and s["near_zero_ok"] and s["bit_equal_frac"] >= 0.98, s
 
 
 @pytest.mark.parametrize("shape", [(4096, 8192, 256), (8192, 8192, 1024), (5000, 3000, 640),
