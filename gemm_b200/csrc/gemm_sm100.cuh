@@ -52,6 +52,9 @@ struct GemmParams {
   int Md, Nd, K;
   int num_m_tiles, num_n_tiles, num_tiles, num_k_blocks;
   int group_m;               // tile rows per raster group (L2 reuse)
+  int tile_rows;             // tall-tile kernels: rows of X per tile (a multiple of 8 between 129
+                             // and kTallRows, chosen so that the tiles spread evenly over the
+                             // SMs); 0 for every other kernel, whose tile height is fixed
   int l2_hints;              // bit 0: X loads evict-last, bit 1: Y loads evict-first,
                              // bit 2: D stores evict-first, bit 3: X loads evict-first,
                              // bit 4: Y loads evict-last (0 = no hints)
@@ -112,11 +115,17 @@ struct GemmParams {
 template <int kCtaGroup_, int BLOCK_N_, int kStages_, int kEpiMode_, int kNHalves_ = 1,
           int kMHalves_ = 1>
 struct GemmConfig {
-  // kMHalves == 2: a CTA's tile is two 128-row blocks of X one below the other that share the Y
-  // operand, each with its own TMEM accumulator.  Made for the skinny shapes whose Y is re-read
-  // by every tile: Y enters the SM once per 256 rows of X instead of once per 128, and one CTA
-  // per SM leaves room for a deep ring.  Whole tiles only (no stream-K), direct-store epilogue.
+  // kMHalves == 2 ("tall tile"): a CTA's tile is up to kTallRows rows of X - one 128-row block
+  // and a second, partly filled one below it - that share the Y operand, each block with its own
+  // TMEM accumulator.  Made for the skinny, HBM-bound shapes: the tile height is a run-time value
+  // (GemmParams::tile_rows) picked so that the rows of X spread evenly over all SMs (28672 rows on
+  // 148 SMs: 200 rows each on 144 of them, instead of 128-row tiles two to some SMs and one to
+  // others), Y enters an SM once per tile instead of once per 128 rows, and one CTA per SM leaves
+  // room for a deep ring of the streamed operand.  The second MMA block always spans 128 rows of
+  // shared memory; rows past the tile's height hold stale bytes, their accumulator lanes are
+  // never stored.  Whole tiles only (no stream-K), direct-store epilogue.
   static constexpr int kMHalves = kMHalves_;
+  static constexpr int kTallRows = 208;
   static constexpr int kCtaGroup = kCtaGroup_;
   static constexpr int BLOCK_N = BLOCK_N_;           // UMMA N
   // kNHalves == 2: the tile is two UMMA-N-wide halves side by side that share the X operand, each
@@ -134,7 +143,7 @@ struct GemmConfig {
   static constexpr int UMMA_K = 16;
   static constexpr int LOAD_N = BLOCK_N / kCtaGroup;  // rows of Y each CTA fetches
   static constexpr int SMEM_X_HALF = BLOCK_M * BLOCK_K * 2;
-  static constexpr int SMEM_X = kMHalves * SMEM_X_HALF;
+  static constexpr int SMEM_X = (kMHalves == 2) ? kTallRows * BLOCK_K * 2 : SMEM_X_HALF;
   static constexpr int SMEM_Y_HALF = LOAD_N * BLOCK_K * 2;
   static constexpr int SMEM_Y = kNHalves * SMEM_Y_HALF;
   static constexpr int SMEM_STAGE = SMEM_X + SMEM_Y;
@@ -672,7 +681,12 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
           pace_wave(p, seg_idx, num_workers, lane);
         int tm, tn;
         tile_coords(p, seg.tile, tm, tn);
-        const int row_x = tm * Cfg::TILE_M + static_cast<int>(cta_rank) * Cfg::BLOCK_M;
+        const int row_x = (Cfg::kMHalves == 2 ? tm * p.tile_rows : tm * Cfg::TILE_M) +
+                          static_cast<int>(cta_rank) * Cfg::BLOCK_M;
+        // Bytes one stage receives: the X box of a tall tile is tile_rows high.
+        const uint32_t stage_bytes = (Cfg::kMHalves == 2)
+            ? static_cast<uint32_t>(p.tile_rows) * (Cfg::BLOCK_K * 2) + Cfg::SMEM_Y
+            : static_cast<uint32_t>(Cfg::SMEM_STAGE);
         const int row_y = tn * Cfg::TILE_N + static_cast<int>(cta_rank) * Cfg::LOAD_N;
         const int kb_end = seg.kb_begin + seg.kb_count;
         // Only the producer knows the direction: the MMA warp consumes ring slots in order and
@@ -696,7 +710,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
           if (elect_one()) {
             const int c0 = (reverse_k ? (seg.kb_begin + kb_end - 1 - kb) : kb) * Cfg::BLOCK_K;
             if (kCtaGroup == 1) {
-              mbar_arrive_expect_tx(full_bar + 8 * stage, Cfg::SMEM_STAGE);
+              mbar_arrive_expect_tx(full_bar + 8 * stage, stage_bytes);
               if (hint_x) tma_load_2d_hint(sx, &tmap_x, full_bar + 8 * stage, c0, row_x, pol_x);
               else tma_load_2d(sx, &tmap_x, full_bar + 8 * stage, c0, row_x);
 #pragma unroll
@@ -936,7 +950,11 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
       // read its share, and the index arithmetic alone was ~1500 cycles of that.
       int tm, tn;
       tile_coords(p, seg.tile, tm, tn);
-      const int row0_tile = tm * Cfg::TILE_M + static_cast<int>(cta_rank) * Cfg::BLOCK_M;
+      const int row0_tile = (Cfg::kMHalves == 2 ? tm * p.tile_rows : tm * Cfg::TILE_M) +
+                            static_cast<int>(cta_rank) * Cfg::BLOCK_M;
+      // Rows of D this tile owns end here (tall tiles: the second block is only partly the
+      // tile's; everything else: the matrix edge).
+      const int row_limit = (Cfg::kMHalves == 2) ? min(p.Md, row0_tile + p.tile_rows) : p.Md;
       const int col0 = tn * Cfg::TILE_N;
       const uint32_t taddr_tile = tmem_base + ((quad * 32u) << 16) + acc * Cfg::kAccumCols;
       const int row0 = row0_tile;            // (the direct-store walk shadows these per M-half)
@@ -1322,11 +1340,11 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
 #pragma unroll
             for (int m = static_cast<int>(lane >> 2); m < kDC; m += 8) {
               const int colm = col + m;
-              if (colm >= p.Nd || n0 >= p.Md) continue;
+              if (colm >= p.Nd || n0 >= row_limit) continue;
               const long long off = static_cast<long long>(colm) * p.out_stride_c + n0;
               uint32_t v[4];
               ld_shared_v4(stg + static_cast<uint32_t>(m) * 64u + (lane & 3u) * 16u, v);
-              if (n0 + 8 <= p.Md) {
+              if (n0 + 8 <= row_limit) {
                 if (off + 8 > p.out_span) {
                   report_error(p, abort_flag, kDevBounds, seg_idx, 3);
                 } else {
@@ -1334,14 +1352,14 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
                 }
               } else {
                 const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(v);
-                for (int j = 0; j < 8 && n0 + j < p.Md; ++j) {
+                for (int j = 0; j < 8 && n0 + j < row_limit; ++j) {
                   if (off + j < p.out_span) p.out[off + j] = e[j];
                 }
               }
             }
           } else
           if (p.out32 != nullptr) {
-            if (row < p.Md && col < p.Nd) {
+            if (row < row_limit && col < p.Nd) {
               const int last_col = min(col + kDC - 1, p.Nd - 1);
               const long long last = static_cast<long long>(row) * p.out_stride_r +
                                      static_cast<long long>(last_col) * p.out_stride_c;
@@ -1363,7 +1381,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
               }
             }
           } else
-          if (row < p.Md && col < p.Nd) {
+          if (row < row_limit && col < p.Nd) {
             const int last_col = min(col + kDC - 1, p.Nd - 1);
             const long long last = static_cast<long long>(row) * p.out_stride_r +
                                    static_cast<long long>(last_col) * p.out_stride_c;

@@ -109,13 +109,14 @@ const KernelEntry* kernel_table(int* count) {
       make_entry<GemmConfig<1, 64, 4, kEpiDirect>>(),
       make_entry<GemmConfig<1, 32, 5, kEpiDirect>>(),
       make_entry<GemmConfig<1, 16, 5, kEpiDirect>>(),
-      // Tall tiles: 256 rows of X per CTA (two 128-row blocks sharing Y), one CTA per SM, ring
-      // filled to 227 KB.  Same use as the four above - one resident wave of whole tiles - with
-      // Y entering the SM once per 256 rows and more bytes of the streamed operand in flight.
-      make_entry<GemmConfig<1, 128, 4, kEpiDirect, 1, 2>>(),
-      make_entry<GemmConfig<1, 64, 5, kEpiDirect, 1, 2>>(),
-      make_entry<GemmConfig<1, 32, 6, kEpiDirect, 1, 2>>(),
-      make_entry<GemmConfig<1, 16, 6, kEpiDirect, 1, 2>>(),
+      // Tall tiles: up to 208 rows of X per CTA (a 128-row block and a partly filled one sharing
+      // Y), one CTA per SM, ring filled to 227 KB.  Same use as the four above - one resident
+      // wave of whole tiles - with the rows spread evenly over the SMs, Y entering an SM once per
+      // tile and more bytes of the streamed operand in flight.
+      make_entry<GemmConfig<1, 128, 5, kEpiDirect, 1, 2>>(),
+      make_entry<GemmConfig<1, 64, 6, kEpiDirect, 1, 2>>(),
+      make_entry<GemmConfig<1, 32, 7, kEpiDirect, 1, 2>>(),
+      make_entry<GemmConfig<1, 16, 7, kEpiDirect, 1, 2>>(),
   };
   *count = static_cast<int>(sizeof(table) / sizeof(table[0]));
   return table;
@@ -302,7 +303,8 @@ struct Plan {
   int cta_group = 1, block_n = 256, epi = kEpiTmaStore;
   int halves = 1;           // 2: 256 x 512 pair tile (two UMMA-N halves sharing X)
   int per_sm = 1;           // 2: half-size rings, two CTAs per SM, one whole tile each
-  int mhalves = 1;          // 2: tall tiles, 256 rows of X per CTA sharing Y, one whole tile each
+  int mhalves = 1;          // 2: tall tiles sharing Y, one whole tile per CTA
+  int tile_rows = 0;        // tall tiles: rows of X per tile (multiple of 8, 136..208)
   bool stream_k = false;
   int sk_first_tile = 0;    // tiles below are handed out round-robin, tiles from here on are cut
   int sk_splits = 0;        // > 0: uniform k-chunks per cut tile (large kernels)
@@ -432,28 +434,43 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
   p.block_n = block_n;
   p.cta_group = cta_group;
   p.epi = epi;
-  // Skinny shapes with more 128-row tiles than SMs but at most two per SM (decode: 224 on 148)
-  // run as ONE wave of whole tiles: every CTA streams its rows of X over all of K, nothing is
-  // cut, nothing has to be summed at the end.  Two kernels can do that.  Tall tiles (the default):
-  // 256 rows of X per CTA, one CTA per SM - cuBLAS' choice for M=16 has the same shape
-  // (nvjet_tst_256x16: 112 whole tiles of 256 rows).  The small operand enters an SM once per 256
-  // rows instead of once per 128 (at M=128 it is as large as the streamed one: 8 MB -> 6 MB into
-  // the SMs that carried two tiles), and a ring that fills the SM.  Or 128-row tiles with two
-  // CTAs per SM and half-size rings.  Tuning key 7: -1 tall tiles when they fit in one wave,
-  // 0 neither (stream-K), 1 two CTAs per SM, 2 tall tiles even where 128-row tiles would fit.
-  int mhalves = 1;
+  // Skinny shapes with more 128-row tiles than SMs (decode: 224 on 148) run as ONE wave of whole
+  // tiles where that is possible: every CTA streams its rows of X over all of K, nothing is cut,
+  // nothing has to be summed at the end.  Two kernels can do that.
+  //  * Tall tiles (the default): the rows are dealt out evenly, ceil(rows / SMs) rounded up to a
+  //    multiple of 8 per CTA - 200 at 28672 rows, on 144 CTAs - as long as that is at most 208
+  //    (a 128-row MMA block and a partly used second one; cuBLAS' M=16 kernel is of the same
+  //    family: nvjet_tst_256x16, 112 whole tiles of 256 rows).  Every SM then has loads of the
+  //    streamed operand in flight (its latency under load is about 3 us, so the bytes in flight
+  //    are what sets the rate), the small operand enters an SM once per tile instead of once per
+  //    128 rows (at M=128 it is as large as the streamed one), and one CTA per SM has the whole
+  //    227 KB for its ring.
+  //  * 128-row tiles with two CTAs per SM and half-size rings, when there are at most two such
+  //    tiles per SM and the tall tiles would have to be higher than 208 rows.
+  // Tuning key 7: -1 as described, 0 neither (stream-K), 1 two CTAs per SM whenever the kernel
+  // exists and the tiles fit, 2 tall tiles for any row count up to 208 rows per SM.
+  int mhalves = 1, tile_rows = 0;
+  bool two_per_sm_auto = false;
   {
-    const int64_t tiles128 = ((md + 127) / 128) * ((nd + block_n - 1) / block_n);
-    const int64_t tiles256 = ((md + 255) / 256) * ((nd + block_n - 1) / block_n);
-    const bool eligible = epi == kEpiDirect && cta_group == 1 && block_n <= kResidentMaxColumns &&
-                          ov.stream_k <= 0 && ov.max_ctas <= 0 && (K + 63) / 64 >= 16 &&
-                          tiles256 <= sm_count;
-    if (eligible && ((ov.tuning[7] < 0 && tiles128 > sm_count && tiles128 <= 2ll * sm_count) ||
-                     ov.tuning[7] == 2))
+    const int64_t n_tiles = (nd + block_n - 1) / block_n;
+    const int64_t tiles128 = ((md + 127) / 128) * n_tiles;
+    const int64_t share = (md * n_tiles + sm_count - 1) / sm_count;      // rows per SM, evenly
+    const int64_t rows = std::max<int64_t>(136, (share + 7) / 8 * 8);
+    const bool one_wave_ok = epi == kEpiDirect && cta_group == 1 &&
+                             block_n <= kResidentMaxColumns && ov.stream_k <= 0 &&
+                             ov.max_ctas <= 0 && (K + 63) / 64 >= 16;
+    const bool tall_fits = rows <= 208 && ((md + rows - 1) / rows) * n_tiles <= sm_count;
+    if (one_wave_ok && tall_fits &&
+        ((ov.tuning[7] < 0 && tiles128 > sm_count) || ov.tuning[7] == 2)) {
       mhalves = 2;
+      tile_rows = static_cast<int>(rows);
+    } else if (one_wave_ok && ov.tuning[7] < 0 && tiles128 > sm_count && tiles128 <= 2ll * sm_count) {
+      two_per_sm_auto = true;
+    }
   }
   p.mhalves = mhalves;
-  const int tile_m = 128 * cta_group * mhalves;
+  p.tile_rows = tile_rows;
+  const int tile_m = mhalves == 2 ? tile_rows : 128 * cta_group;
   p.num_m_tiles = static_cast<int>((md + tile_m - 1) / tile_m);
   const int tile_n = block_n * p.halves;
   p.num_n_tiles = static_cast<int>((nd + tile_n - 1) / tile_n);
@@ -466,9 +483,9 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
   // (K=4096: 48.2 -> 40.2 us), M=128 87.8 -> 82.8 us, M=96 91.6 -> 84.3 us.  Picked only on
   // request (tuning key 7 = 1), whenever the kernel exists and all tiles fit at once.
   int per_sm = 1;
-  if (epi == kEpiDirect && cta_group == 1 && mhalves == 1 && ov.tuning[7] == 1 && ov.stream_k <= 0 &&
+  if (epi == kEpiDirect && cta_group == 1 && mhalves == 1 && ov.stream_k <= 0 &&
       ov.max_ctas <= 0 && tiles <= 2ll * sm_count && (K + 63) / 64 >= 16 &&
-      block_n <= kResidentMaxColumns)
+      block_n <= kResidentMaxColumns && (ov.tuning[7] == 1 || two_per_sm_auto))
     per_sm = 2;
   p.per_sm = per_sm;
   p.kernel = find_kernel(cta_group, block_n, epi, p.halves, per_sm, mhalves, &p.kernel_index);
@@ -725,7 +742,8 @@ int gemm_device(const void* A, const void* B, void* C, int64_t M, int64_t N, int
   const int promo = (t_override.tuning[5] >= 0 && t_override.tuning[5] < 3)
       ? -1 - t_override.tuning[5] : 0;
   rc = get_tensor_map(X, static_cast<uint64_t>(K), static_cast<uint64_t>(plan.Md),
-                      static_cast<uint64_t>(ldx) * 2, 128u * plan.mhalves, promo, &mx);
+                      static_cast<uint64_t>(ldx) * 2,
+                      plan.mhalves == 2 ? static_cast<uint32_t>(plan.tile_rows) : 128u, promo, &mx);
   if (rc != NEOGEMM_OK) return rc;
   rc = get_tensor_map(Y, static_cast<uint64_t>(K), static_cast<uint64_t>(plan.Nd),
                       static_cast<uint64_t>(ldy) * 2,
@@ -747,6 +765,7 @@ int gemm_device(const void* A, const void* B, void* C, int64_t M, int64_t N, int
   params.num_tiles = plan.num_tiles;
   params.num_k_blocks = plan.num_k_blocks;
   params.group_m = plan.group_m;
+  params.tile_rows = plan.tile_rows;
   // Skinny shapes with a single tile column read every row panel of X exactly once: mark those
   // loads evict-first and the small, endlessly re-read Y evict-last, so that the stream does not
   // push Y and the stream-K partials out of L2 (measured: 5 % at M=16, 9 % at M=128 on the decode
@@ -1461,7 +1480,8 @@ int neogemm_bf16_nt_noalloc(const void* A, const void* B, void* C, int64_t M, in
   CUtensorMap mx, my, md;
   std::memset(&md, 0, sizeof(md));
   rc = encode_map_uncached(X, static_cast<uint64_t>(K), static_cast<uint64_t>(plan.Md),
-                           static_cast<uint64_t>(ldx) * 2, 128u * plan.mhalves, 0, &mx);
+                           static_cast<uint64_t>(ldx) * 2,
+                           plan.mhalves == 2 ? static_cast<uint32_t>(plan.tile_rows) : 128u, 0, &mx);
   if (rc != NEOGEMM_OK) return rc;
   rc = encode_map_uncached(Y, static_cast<uint64_t>(K), static_cast<uint64_t>(plan.Nd),
                            static_cast<uint64_t>(ldy) * 2,
@@ -1483,6 +1503,7 @@ int neogemm_bf16_nt_noalloc(const void* A, const void* B, void* C, int64_t M, in
   params.num_tiles = plan.num_tiles;
   params.num_k_blocks = plan.num_k_blocks;
   params.group_m = plan.group_m;
+  params.tile_rows = plan.tile_rows;
   params.l2_hints = (plan.epi == kEpiDirect && plan.num_n_tiles == 1) ? 24 : kDefaultTuning[0];
   params.epi_wait_hint_ns = kDefaultTuning[1];
   params.main_wait_hint_ns = kDefaultTuning[2];

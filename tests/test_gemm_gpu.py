@@ -34,9 +34,9 @@ def test_config_8192_cube():
 def test_config_decode_shapes(M):
     stats, cfg = run_case(M, 28672, 8192)
     assert cfg["swap"] == 1, cfg
-    # one wave of 112 whole tall tiles (256 rows of B each), one CTA per SM
-    stages = 6 if M <= 32 else (5 if M <= 64 else 4)
-    assert (cfg["stream_k"], cfg["ctas"], cfg["tiles"], cfg["stages"]) == (0, 112, 112, stages), cfg
+    # one wave of 144 whole tall tiles (200 rows of B each), one CTA per SM
+    stages = 7 if M <= 32 else (6 if M <= 64 else 5)
+    assert (cfg["stream_k"], cfg["ctas"], cfg["tiles"], cfg["stages"]) == (0, 144, 144, stages), cfg
     # the other one-wave plan: 224 tiles of 128 rows, two CTAs to an SM
     stats, cfg = run_case(M, 28672, 8192, tuning={"two_ctas_per_sm": 1})
     half = 5 if M <= 32 else (4 if M <= 64 else 3)
@@ -47,17 +47,19 @@ def test_config_decode_shapes(M):
 
 
 @pytest.mark.parametrize("shape", [(16, 28672, 8192), (8, 19000, 1024), (24, 30000, 2048),
-                                   (64, 28672, 4096), (40, 20008, 1536), (1, 37000, 1024),
+                                   (64, 28672, 4096), (40, 20008, 1536), (1, 30000, 1024),
                                    (100, 20000, 2048), (128, 28672, 1024), (128, 257, 1024),
-                                   (72, 511, 1088)])
+                                   (72, 511, 1088), (16, 30784, 1024), (48, 30001, 1024)])
 def test_tall_tiles_whole_wave(shape):
-    # 256 rows of the long operand per CTA, two accumulators sharing the short operand (forced,
-    # so that shapes the launcher would not pick on its own run too): ragged rows (a second half
-    # that is partly or wholly out of range), ragged K, both layouts, launch-to-launch determinism.
+    # 136 to 208 rows of the long operand per CTA (its even share of the rows, a multiple of 8),
+    # two accumulators sharing the short operand (forced, so that shapes the launcher would not
+    # pick on its own run too): ragged rows (a second block that is partly or wholly out of
+    # range), ragged K, both layouts, launch-to-launch determinism.
     stats, cfg = run_case(*shape, tuning={"two_ctas_per_sm": 2})
     rows = shape[1]
-    assert cfg["stream_k"] == 0 and cfg["ctas"] == cfg["tiles"] == (rows + 255) // 256, cfg
-    assert cfg["stages"] in (4, 5, 6), cfg
+    per_cta = max(136, (-(-rows // 148) + 7) // 8 * 8)
+    assert cfg["stream_k"] == 0 and cfg["ctas"] == cfg["tiles"] == -(-rows // per_cta), cfg
+    assert cfg["stages"] in (5, 6, 7), cfg
     run_case(*shape, tuning={"two_ctas_per_sm": 2}, col_major=True)
     A, B = make_problem(*shape, seed=6)
     dA, dB = A.cuda(), B.cuda()

@@ -75,30 +75,37 @@ def test_data_parallel_and_mixed_plans_cover_the_problem(shape, col_major):
 
 @pytest.mark.parametrize("M", [8, 16, 32, 64, 128])
 def test_decode_shapes_run_as_one_wave_of_whole_tiles(M):
-    # 28672 rows of B on 148 SMs: 112 tall tiles (256 rows each, one CTA per SM), one whole tile
-    # per CTA, nothing cut.
+    # 28672 rows of B on 148 SMs: ceil(28672 / 148) = 194 -> 200 rows per CTA (a multiple of 8),
+    # 144 tall tiles, one whole tile per CTA, nothing cut.
     p, segs = plan(M, 28672, 8192)
-    stages = 6 if M <= 32 else (5 if M <= 64 else 4)
+    stages = 7 if M <= 32 else (6 if M <= 64 else 5)
     assert (p["swap"], p["stream_k"], p["cta_group"], p["stages"]) == (1, 0, 1, stages)
-    assert p["tiles"] == 112 and p["ctas"] == 112 and p["max_contrib"] == 0
+    assert p["tiles"] == 144 and p["ctas"] == 144 and p["max_contrib"] == 0
     check_cover(p, segs)
-    assert sorted(s[0] for s in segs) == list(range(112)) and all(s[3] == 128 for s in segs)
-    # not when 128-row tiles fit one per SM, when there are more than two per SM, or for short K
+    assert sorted(s[0] for s in segs) == list(range(144)) and all(s[3] == 128 for s in segs)
+    # not when 128-row tiles fit one per SM, when a CTA's share exceeds 208 rows and there are
+    # more than two 128-row tiles per SM, or for short K
     assert plan(M, 148 * 128, 8192)[0]["ctas"] == 148
     assert plan(M, 297 * 128, 8192)[0]["ctas"] == 148
     assert plan(M, 28672, 512)[0]["ctas"] == 148
-    # forced on (also below one 128-row tile per SM) and off
+    # up to 208 rows per SM: 148 * 208 = 30784 rows
+    p2, _ = plan(M, 30784, 8192)
+    assert (p2["stream_k"], p2["tiles"], p2["ctas"], p2["stages"]) == (0, 148, 148, stages)
+    # forced on (also below one 128-row tile per SM: 136-row tiles) and off
     p2, _ = plan(M, 100 * 128, 8192, tuning={7: 2})
-    assert (p2["tiles"], p2["ctas"], p2["stages"]) == (50, 50, stages)
+    assert (p2["tiles"], p2["ctas"], p2["stages"]) == (95, 95, stages)
     p, segs = plan(M, 28672, 8192, tuning={7: 0})
     assert (p["stream_k"], p["ctas"]) == (1, 148)
     check_cover(p, segs)
-    # the other one-wave plan: 224 tiles of 128 rows, two CTAs per SM with half-size rings
-    p, segs = plan(M, 28672, 8192, tuning={7: 1})
+    # the other one-wave plan: 128-row tiles, two CTAs per SM with half-size rings - on request,
+    # and on its own between 208 and 256 rows per SM
     half_stages = 5 if M <= 32 else (4 if M <= 64 else 3)
+    p, segs = plan(M, 28672, 8192, tuning={7: 1})
     assert (p["stream_k"], p["tiles"], p["ctas"], p["stages"]) == (0, 224, 224, half_stages)
     check_cover(p, segs)
     assert plan(M, 100 * 128, 8192, tuning={7: 1})[0]["stages"] == half_stages
+    p, segs = plan(M, 280 * 128, 8192)
+    assert (p["stream_k"], p["tiles"], p["ctas"], p["stages"]) == (0, 280, 280, half_stages)
 
 
 @pytest.mark.parametrize("M", [16, 64, 128])
