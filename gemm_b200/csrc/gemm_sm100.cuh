@@ -123,7 +123,9 @@ struct GemmConfig {
   // others), Y enters an SM once per tile instead of once per 128 rows, and one CTA per SM leaves
   // room for a deep ring of the streamed operand.  The second MMA block always spans 128 rows of
   // shared memory; rows past the tile's height hold stale bytes, their accumulator lanes are
-  // never stored.  Whole tiles only (no stream-K), direct-store epilogue.
+  // never stored.  Whole tiles only (no stream-K), direct-store epilogue.  With kCtaGroup == 2 two
+  // such CTAs share Y as well: each loads half of its rows, the pair's MMA reads both halves, so Y
+  // takes half as much of every ring slot and the ring of the streamed operand gets deeper.
   static constexpr int kMHalves = kMHalves_;
   static constexpr int kTallRows = 208;
   static constexpr int kCtaGroup = kCtaGroup_;
@@ -182,9 +184,9 @@ struct GemmConfig {
   static_assert(kCtaGroup == 1 || kTmemCols == 512,
                 "pair mode allocates all of tensor memory so both CTAs get column 0");
   static_assert(SMEM_TOTAL <= 232448, "exceeds 227 KB of shared memory per CTA");
-  static_assert(kMHalves == 1 || (kMHalves == 2 && kCtaGroup == 1 && kNHalves == 1 &&
-                                  kEpiMode == kEpiDirect && 2 * kAccumCols <= 512),
-                "two M-halves: single-CTA direct-store kernels with both accumulator sets in TMEM");
+  static_assert(kMHalves == 1 || (kMHalves == 2 && kNHalves == 1 && kEpiMode == kEpiDirect &&
+                                  2 * kAccumCols <= 512),
+                "two M-halves: direct-store kernels with both accumulator sets in TMEM");
   // The last tile's store epilogue borrows one 4 KB box buffer per box from the idle ring.
   static_assert(kEpiMode != kEpiTmaStore ||
                     kEpiWarps * 4 * SMEM_EPI_WARP_BUF <= kStages * SMEM_STAGE,
@@ -681,8 +683,10 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
           pace_wave(p, seg_idx, num_workers, lane);
         int tm, tn;
         tile_coords(p, seg.tile, tm, tn);
-        const int row_x = (Cfg::kMHalves == 2 ? tm * p.tile_rows : tm * Cfg::TILE_M) +
-                          static_cast<int>(cta_rank) * Cfg::BLOCK_M;
+        // Tall tiles: every CTA (of a pair, too) owns tile_rows consecutive rows of X.
+        const int row_x = (Cfg::kMHalves == 2)
+            ? (tm * kCtaGroup + static_cast<int>(cta_rank)) * p.tile_rows
+            : tm * Cfg::TILE_M + static_cast<int>(cta_rank) * Cfg::BLOCK_M;
         // Bytes one stage receives: the X box of a tall tile is tile_rows high.
         const uint32_t stage_bytes = (Cfg::kMHalves == 2)
             ? static_cast<uint32_t>(p.tile_rows) * (Cfg::BLOCK_K * 2) + Cfg::SMEM_Y
@@ -721,7 +725,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
                 else tma_load_2d(dst, &tmap_y, full_bar + 8 * stage, c0, ry);
               }
             } else {
-              if (is_leader) mbar_arrive_expect_tx(full_bar + 8 * stage, 2 * Cfg::SMEM_STAGE);
+              if (is_leader) mbar_arrive_expect_tx(full_bar + 8 * stage, 2 * stage_bytes);
               if (hint_x) tma_load_2d_pair_hint(sx, &tmap_x, leader_full + 8 * stage, c0, row_x, pol_x);
               else tma_load_2d_pair(sx, &tmap_x, leader_full + 8 * stage, c0, row_x);
 #pragma unroll
@@ -950,8 +954,9 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
       // read its share, and the index arithmetic alone was ~1500 cycles of that.
       int tm, tn;
       tile_coords(p, seg.tile, tm, tn);
-      const int row0_tile = (Cfg::kMHalves == 2 ? tm * p.tile_rows : tm * Cfg::TILE_M) +
-                            static_cast<int>(cta_rank) * Cfg::BLOCK_M;
+      const int row0_tile = (Cfg::kMHalves == 2)
+          ? (tm * kCtaGroup + static_cast<int>(cta_rank)) * p.tile_rows
+          : tm * Cfg::TILE_M + static_cast<int>(cta_rank) * Cfg::BLOCK_M;
       // Rows of D this tile owns end here (tall tiles: the second block is only partly the
       // tile's; everything else: the matrix edge).
       const int row_limit = (Cfg::kMHalves == 2) ? min(p.Md, row0_tile + p.tile_rows) : p.Md;

@@ -117,6 +117,9 @@ const KernelEntry* kernel_table(int* count) {
       make_entry<GemmConfig<1, 64, 6, kEpiDirect, 1, 2>>(),
       make_entry<GemmConfig<1, 32, 7, kEpiDirect, 1, 2>>(),
       make_entry<GemmConfig<1, 16, 7, kEpiDirect, 1, 2>>(),
+      // Tall tiles on CTA pairs: the small operand is split between the two CTAs' rings.
+      make_entry<GemmConfig<2, 128, 6, kEpiDirect, 1, 2>>(),
+      make_entry<GemmConfig<2, 64, 7, kEpiDirect, 1, 2>>(),
   };
   *count = static_cast<int>(sizeof(table) / sizeof(table[0]));
   return table;
@@ -464,13 +467,18 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
         ((ov.tuning[7] < 0 && tiles128 > sm_count) || ov.tuning[7] == 2)) {
       mhalves = 2;
       tile_rows = static_cast<int>(rows);
+      // From 64 columns on the small operand is worth splitting between two CTAs: pairs of
+      // tall tiles (2 x tile_rows rows per pair), provided the pairs still fit in one wave.
+      const int64_t pair_tiles = ((md + 2 * rows - 1) / (2 * rows)) * n_tiles;
+      if (block_n >= 64 && ov.cta_group != 1 && 2 * pair_tiles <= sm_count) cta_group = 2;
     } else if (one_wave_ok && ov.tuning[7] < 0 && tiles128 > sm_count && tiles128 <= 2ll * sm_count) {
       two_per_sm_auto = true;
     }
   }
   p.mhalves = mhalves;
   p.tile_rows = tile_rows;
-  const int tile_m = mhalves == 2 ? tile_rows : 128 * cta_group;
+  p.cta_group = cta_group;   // (pairs of tall tiles were decided just above)
+  const int tile_m = mhalves == 2 ? tile_rows * cta_group : 128 * cta_group;
   p.num_m_tiles = static_cast<int>((md + tile_m - 1) / tile_m);
   const int tile_n = block_n * p.halves;
   p.num_n_tiles = static_cast<int>((nd + tile_n - 1) / tile_n);

@@ -34,9 +34,15 @@ def test_config_8192_cube():
 def test_config_decode_shapes(M):
     stats, cfg = run_case(M, 28672, 8192)
     assert cfg["swap"] == 1, cfg
-    # one wave of 144 whole tall tiles (200 rows of B each), one CTA per SM
-    stages = 7 if M <= 32 else (6 if M <= 64 else 5)
-    assert (cfg["stream_k"], cfg["ctas"], cfg["tiles"], cfg["stages"]) == (0, 144, 144, stages), cfg
+    # one wave of whole tall tiles (200 rows of B per CTA), one CTA per SM on 144 SMs; from 64
+    # columns on the CTAs work in pairs that share the small operand
+    group = 2 if M >= 64 else 1
+    stages = 7 if M <= 64 else 6
+    assert (cfg["stream_k"], cfg["ctas"], cfg["tiles"], cfg["stages"], cfg["cta_group"]) == \
+        (0, 144, 144 // group, stages, group), cfg
+    if group == 2:
+        stats, cfg = run_case(M, 28672, 8192, override=dict(cta_group=1))
+        assert (cfg["stream_k"], cfg["ctas"], cfg["tiles"], cfg["cta_group"]) == (0, 144, 144, 1), cfg
     # the other one-wave plan: 224 tiles of 128 rows, two CTAs to an SM
     stats, cfg = run_case(M, 28672, 8192, tuning={"two_ctas_per_sm": 1})
     half = 5 if M <= 32 else (4 if M <= 64 else 3)
@@ -58,8 +64,13 @@ def test_tall_tiles_whole_wave(shape):
     stats, cfg = run_case(*shape, tuning={"two_ctas_per_sm": 2})
     rows = shape[1]
     per_cta = max(136, (-(-rows // 148) + 7) // 8 * 8)
-    assert cfg["stream_k"] == 0 and cfg["ctas"] == cfg["tiles"] == -(-rows // per_cta), cfg
-    assert cfg["stages"] in (5, 6, 7), cfg
+    group = cfg["cta_group"]
+    assert group == (2 if shape[0] > 32 else 1), cfg
+    assert cfg["stream_k"] == 0 and cfg["tiles"] == -(-rows // (per_cta * group)), cfg
+    assert cfg["ctas"] == cfg["tiles"] * group and cfg["stages"] in (5, 6, 7), cfg
+    if group == 2:   # the same tiles on single CTAs
+        stats, cfg = run_case(*shape, tuning={"two_ctas_per_sm": 2}, override=dict(cta_group=1))
+        assert cfg["cta_group"] == 1 and cfg["ctas"] == cfg["tiles"] == -(-rows // per_cta), cfg
     run_case(*shape, tuning={"two_ctas_per_sm": 2}, col_major=True)
     A, B = make_problem(*shape, seed=6)
     dA, dB = A.cuda(), B.cuda()

@@ -77,12 +77,18 @@ def test_data_parallel_and_mixed_plans_cover_the_problem(shape, col_major):
 def test_decode_shapes_run_as_one_wave_of_whole_tiles(M):
     # 28672 rows of B on 148 SMs: ceil(28672 / 148) = 194 -> 200 rows per CTA (a multiple of 8),
     # 144 tall tiles, one whole tile per CTA, nothing cut.
+    # From 64 columns on two CTAs pair up and share the small operand: 72 pair tiles of 2 x 200 rows.
     p, segs = plan(M, 28672, 8192)
-    stages = 7 if M <= 32 else (6 if M <= 64 else 5)
-    assert (p["swap"], p["stream_k"], p["cta_group"], p["stages"]) == (1, 0, 1, stages)
-    assert p["tiles"] == 144 and p["ctas"] == 144 and p["max_contrib"] == 0
+    group = 2 if M >= 64 else 1
+    stages = 7 if M <= 64 else 6
+    assert (p["swap"], p["stream_k"], p["cta_group"], p["stages"]) == (1, 0, group, stages)
+    assert p["tiles"] == 144 // group and p["ctas"] == 144 and p["max_contrib"] == 0
     check_cover(p, segs)
-    assert sorted(s[0] for s in segs) == list(range(144)) and all(s[3] == 128 for s in segs)
+    assert sorted(s[0] for s in segs) == list(range(144 // group)) and all(s[3] == 128 for s in segs)
+    # single CTAs on request
+    p1, _ = plan(M, 28672, 8192, override=(1, -1, -1, -1, -1, -1))
+    assert (p1["cta_group"], p1["tiles"], p1["ctas"]) == (1, 144, 144)
+    assert p1["stages"] == (7 if M <= 32 else (6 if M <= 64 else 5))
     # not when 128-row tiles fit one per SM, when a CTA's share exceeds 208 rows and there are
     # more than two 128-row tiles per SM, or for short K
     assert plan(M, 148 * 128, 8192)[0]["ctas"] == 148
@@ -90,10 +96,10 @@ def test_decode_shapes_run_as_one_wave_of_whole_tiles(M):
     assert plan(M, 28672, 512)[0]["ctas"] == 148
     # up to 208 rows per SM: 148 * 208 = 30784 rows
     p2, _ = plan(M, 30784, 8192)
-    assert (p2["stream_k"], p2["tiles"], p2["ctas"], p2["stages"]) == (0, 148, 148, stages)
+    assert (p2["stream_k"], p2["tiles"], p2["ctas"], p2["stages"]) == (0, 148 // group, 148, stages)
     # forced on (also below one 128-row tile per SM: 136-row tiles) and off
     p2, _ = plan(M, 100 * 128, 8192, tuning={7: 2})
-    assert (p2["tiles"], p2["ctas"], p2["stages"]) == (95, 95, stages)
+    assert (p2["tiles"], p2["ctas"], p2["stages"]) == (-(-95 // group), -(-95 // group) * group, stages)
     p, segs = plan(M, 28672, 8192, tuning={7: 0})
     assert (p["stream_k"], p["ctas"]) == (1, 148)
     check_cover(p, segs)
