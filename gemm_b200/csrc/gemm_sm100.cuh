@@ -86,6 +86,10 @@ struct GemmParams {
                              // one per worker (worker w takes chunk w / tiles of tile w % tiles),
                              // instead of one contiguous unit range per worker
   int max_contrib;           // partial slots per tile in `partials`
+  int sk_two_pass;           // 1: contributors of a cut tile only publish their partials; the
+                             // closing sums, the epilogue arithmetic and the stores of those
+                             // tiles are done by splitk_reduce_kernel, launched right behind
+                             // this kernel.  0: the last contributor to arrive finishes the tile.
   // Dynamic tail pool (pure stream-K only; all zero otherwise).  The last dyn_ppt * dyn_piece_kb
   // k-blocks of every tile are not part of any CTA's static range: they form dyn_pieces fixed
   // pieces that CTAs claim from `dyn_counter` as they run out of static work, which evens out
@@ -1027,18 +1031,22 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
           // the fence orders them before the counter increment for every other CTA (cumulativity),
           // so one lane fences instead of thirty-two.  Acquire on the way back, same shape.
           __syncwarp();
-          int* counter = p.tile_counters + counter_idx;
-          int prev = 0;
-          if (lane == 0) {
-            __threadfence();
-            prev = atomicAdd(counter, 1);
-            if (prev == seg.n_contrib - 1) {
+          if (p.sk_two_pass) {
+            finish = false;   // the reduction kernel behind this launch completes the tile
+          } else {
+            int* counter = p.tile_counters + counter_idx;
+            int prev = 0;
+            if (lane == 0) {
               __threadfence();
-              *counter = 0;  // ready for the next launch that uses this workspace
+              prev = atomicAdd(counter, 1);
+              if (prev == seg.n_contrib - 1) {
+                __threadfence();
+                *counter = 0;  // ready for the next launch that uses this workspace
+              }
             }
+            prev = __shfl_sync(0xffffffffu, prev, 0);
+            finish = (prev == seg.n_contrib - 1);
           }
-          prev = __shfl_sync(0xffffffffu, prev, 0);
-          finish = (prev == seg.n_contrib - 1);
         }
       }
 
@@ -1455,6 +1463,106 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
     tmem_dealloc<1>(tmem_base, Cfg::kTmemCols);
   }
   if (threadIdx.x == 0) PhaseTimer(p).stamp(12);
+}
+
+// Second pass of a two-pass split-K launch.  When every tile of a launch is cut into the same
+// number of k-chunks (few wide tiles under a long K: one chunk per CTA fills the machine where
+// whole tiles would use a fraction of it), the GEMM kernel only publishes fp32 partials and this
+// kernel, launched right behind it on the same stream, sums them in contributor order, applies
+// the fused epilogue and stores D.  All SMs take part: a thread owns one row of a tile and eight
+// consecutive columns, so every load of a partial is a coalesced 128-byte line per warp and the
+// sums of different tiles, rows and column groups run in parallel - where a last-arriving
+// contributor summing a 256 x 256 tile alone took longer than the product itself.
+// Partial layout: [tile][contributor][column][row of the tile], as the GEMM kernel writes it.
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const __grid_constant__ GemmParams p, int tile_m, int block_n) {
+  ptx::griddep_launch_dependents();
+  ptx::griddep_wait();   // the partials of the GEMM kernel in front are complete and visible
+  const int n = p.sk_splits;
+  const int groups = block_n / 8;
+  const long long per_tile = static_cast<long long>(tile_m) * groups;
+  const long long total = per_tile * p.num_tiles;
+  const size_t slot = static_cast<size_t>(block_n) * tile_m;
+  for (long long item = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; item < total;
+       item += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int tile = static_cast<int>(item / per_tile);
+    const long long rest = item - tile * per_tile;
+    const int g = static_cast<int>(rest / tile_m);
+    const int r_in_tile = static_cast<int>(rest - static_cast<long long>(g) * tile_m);
+    int tm, tn;
+    tile_coords(p, tile, tm, tn);
+    const int row = tm * tile_m + r_in_tile;
+    const int col = tn * block_n + g * 8;
+    if (row >= p.Md || col >= p.Nd) continue;
+    const float* base = p.partials + static_cast<size_t>(tile) * p.max_contrib * slot +
+                        static_cast<size_t>(g * 8) * tile_m + r_in_tile;
+    float sum[8];
+#pragma unroll 1
+    for (int q0 = 0; q0 < n; q0 += 4) {
+      float t[4][8];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (q0 + k < n) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            t[k][j] = __ldcg(base + static_cast<size_t>(q0 + k) * slot + static_cast<size_t>(j) * tile_m);
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (q0 + k < n) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) sum[j] = (q0 + k == 0) ? t[k][j] : sum[j] + t[k][j];
+        }
+      }
+    }
+    uint32_t r[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) r[j] = __float_as_uint(sum[j]);
+    if (p.fuse) fused_epilogue<8>(r, p, row, col);
+    // D is row-major here (the TMA-store kernels' layout) or any strided layout of the direct
+    // kernels: eight columns of one row.
+    const int last_col = min(col + 7, p.Nd - 1);
+    const long long first = static_cast<long long>(row) * p.out_stride_r +
+                            static_cast<long long>(col) * p.out_stride_c;
+    const long long last = static_cast<long long>(row) * p.out_stride_r +
+                           static_cast<long long>(last_col) * p.out_stride_c;
+    if (last >= p.out_span || first < 0) {
+      if (p.status != nullptr && atomicCAS(p.status, 0, kDevBounds) == 0) {
+        p.status[1] = static_cast<int>(blockIdx.x);
+        p.status[2] = -3;
+        p.status[3] = 3;
+        __threadfence_system();
+      }
+      continue;
+    }
+    const bool full = (col + 8 <= p.Nd) && (p.out_stride_c == 1);
+    if (p.out32 != nullptr) {
+      float* dst = p.out32 + first;
+      if (full && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+        reinterpret_cast<uint4*>(dst)[0] = make_uint4(r[0], r[1], r[2], r[3]);
+        reinterpret_cast<uint4*>(dst)[1] = make_uint4(r[4], r[5], r[6], r[7]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (col + j < p.Nd) dst[static_cast<long long>(j) * p.out_stride_c] = __uint_as_float(r[j]);
+      }
+    } else {
+      __nv_bfloat16* dst = p.out + first;
+      if (full && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(
+            ptx::pack_bf16x2(__uint_as_float(r[0]), __uint_as_float(r[1])),
+            ptx::pack_bf16x2(__uint_as_float(r[2]), __uint_as_float(r[3])),
+            ptx::pack_bf16x2(__uint_as_float(r[4]), __uint_as_float(r[5])),
+            ptx::pack_bf16x2(__uint_as_float(r[6]), __uint_as_float(r[7])));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (col + j < p.Nd)
+            dst[static_cast<long long>(j) * p.out_stride_c] = __float2bfloat16_rn(__uint_as_float(r[j]));
+      }
+    }
+  }
 }
 
 // Self-test of the bounded-wait machinery: one warp waits, with the given limit, on an mbarrier

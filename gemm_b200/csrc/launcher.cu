@@ -58,6 +58,10 @@ constexpr bool kDefaultKAlternate = true;
 constexpr int kPaceMinWaves = 8;
 constexpr int kPaceSlots = 32;
 constexpr int kPaceTimeoutNs = 20000;
+// Microseconds a two-pass split-K launch pays on top of its longest k-chunk: publishing the
+// partials and the reduction kernel behind the GEMM (used when ranking plans; measured:
+// 1024 x 1024 x 8192 in 4 chunks of 32 k-blocks takes 22.6 us where the chunk alone is 13 us).
+constexpr double kTwoPassUs = 9.0;
 // Widest tile (columns) that has a half-size-ring kernel for two CTAs per SM (five ring stages
 // up to 32 columns, four of 24 KB at 64, three of 32 KB at 128) or a tall-tile kernel.
 constexpr int kResidentMaxColumns = 128;
@@ -169,7 +173,7 @@ bool g_encode_looked_up = false;
 
 struct Override {
   int cta_group = -1, block_n = -1, swap = -1, stream_k = -1, group_m = -1, max_ctas = -1;
-  int tuning[11] = {-1, -1, -1, -1, -1, -1, -1, -1, -1, -1, -1};   // see neogemm_set_tuning
+  int tuning[12] = {-1, -1, -1, -1, -1, -1, -1, -1, -1, -1, -1, -1};   // see neogemm_set_tuning
 };
 thread_local Override t_override;
 thread_local int t_last_config[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -311,6 +315,7 @@ struct Plan {
   bool stream_k = false;
   int sk_first_tile = 0;    // tiles below are handed out round-robin, tiles from here on are cut
   int sk_splits = 0;        // > 0: uniform k-chunks per cut tile (large kernels)
+  bool two_pass = false;    // every tile is cut uniformly and a reduction kernel finishes them
   int dyn_ppt = 0, dyn_piece_kb = 0, dyn_static_kb = 0, dyn_pieces = 0;   // dynamic tail pool
   int group_m = 8;
   int num_ctas = 0;
@@ -371,7 +376,11 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
   // Their partials are small (32 KB) and every cut tile has its own finisher, so the closing sums
   // stay short.  Measured: 512 x 512 x 8192 37.8 -> 18.7 us, 256 x 256 x 4096 21.4 -> 15.6 us;
   // with more tiles than an eighth of the SMs the whole tiles win (1536 x 1024 x 3072).
+  // (Only with the two-pass split-K switched off, tuning key 11 = 0: cutting the wide tiles and
+  // summing them in a second kernel is faster still - 512 x 512 x 8192 then runs as 4 pair tiles
+  // in 8 chunks.)
   if (epi == kEpiTmaStore && ov.block_n <= 0 && ov.cta_group <= 0 && ov.stream_k != 0 &&
+      ov.tuning[11] == 0 &&
       ov.tuning[3] != 1 && allow_hybrid && (K + 63) / 64 >= 64 &&
       ((md + 127) / 128) * ((nd + 127) / 128) * 8 <= sm_count) {
     epi = kEpiDirect;
@@ -409,10 +418,27 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
       const int64_t tiles = ((md + tm - 1) / tm) * ((nd + tile_n - 1) / tile_n);
       const int rest = static_cast<int>(tiles % workers);
       double waves = static_cast<double>(tiles / workers);
+      double extra_us = 0.0;
       if (rest > 0) {
-        const int cut = allow_hybrid && ov.stream_k != 0 && c.halves == 1 && tiles >= workers
-            ? hybrid_splits(rest, static_cast<int>(workers), static_cast<int>((K + 63) / 64), 16)
-            : 0;
+        const bool may_cut = allow_hybrid && ov.stream_k != 0 && c.halves == 1;
+        int cut = 0;
+        if (may_cut && tiles >= workers) {
+          cut = hybrid_splits(rest, static_cast<int>(workers), static_cast<int>((K + 63) / 64), 16);
+        } else if (may_cut && ov.tuning[11] != 0) {
+          // fewer tiles than workers: every tile in `cut` chunks, summed by a second kernel -
+          // where that beats the whole tiles (the schedule below applies the same test)
+          cut = hybrid_splits(rest, static_cast<int>(workers), static_cast<int>((K + 63) / 64), 8);
+          if (cut > 0) {
+            const double t_whole = 2.0 * 128.0 * c.cta_group * static_cast<double>(c.block_n) *
+                                   static_cast<double>(K) /
+                                   (c.speed * 1e6 / std::max(1, sm_count / c.cta_group));
+            if (ov.stream_k < 0 &&
+                t_whole / cut * 1.05 + kTwoPassUs >= std::max(t_whole, kEpilogueUs))
+              cut = 0;
+            else
+              extra_us = kTwoPassUs;
+          }
+        }
         waves += cut > 0 ? 1.0 / cut + 0.05 : 1.0;
       }
       // Time of one tile on one worker at that kernel's throughput, in microseconds, plus what
@@ -422,7 +448,7 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
       const double t_main = 2.0 * static_cast<double>(tm) * static_cast<double>(tile_n) *
                             static_cast<double>(K) / (c.speed * 1e6 / workers_full);
       const double t_tile = (c.halves == 2) ? t_main + kHandOverUs : std::max(t_main, kEpilogueUs);
-      const double cost = waves * t_tile;
+      const double cost = waves * t_tile + extra_us;
       if (best == 0.0 || cost < best) {
         best = cost;
         best_group = c.cta_group;
@@ -545,10 +571,25 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
     // Only behind at least one whole wave: the cut tiles are done first, and their closing
     // reduction then hides under the whole tiles that follow.
     const int rest = p.num_tiles % workers;
-    sk_splits = allow_hybrid && ov.stream_k != 0 && p.halves == 1 && p.num_tiles >= workers
-        ? hybrid_splits(rest, workers, p.num_k_blocks, 16) : 0;
+    if (p.num_tiles >= workers) {
+      sk_splits = allow_hybrid && ov.stream_k != 0 && p.halves == 1
+          ? hybrid_splits(rest, workers, p.num_k_blocks, 16) : 0;
+      sk_first = p.num_tiles - rest;
+    } else if (allow_hybrid && ov.stream_k != 0 && p.halves == 1 && ov.tuning[11] != 0) {
+      // Fewer tiles than workers (few wide tiles under a long K): every tile in the same number
+      // of k-chunks, one per worker; the reduction kernel behind the launch sums them.  Only
+      // where the shorter main loop pays for the second pass (or on request).
+      sk_splits = hybrid_splits(p.num_tiles, workers, p.num_k_blocks, 8);
+      sk_first = 0;
+      const double speed = cta_group == 2 ? (block_n == 256 ? 1570.0 : 975.0)
+                                          : (block_n == 256 ? 1430.0 : 1170.0);
+      const double t_tile = 2.0 * tile_m * static_cast<double>(block_n) * static_cast<double>(K) /
+                            (speed * 1e6 / std::max(1, sm_count / cta_group));
+      if (sk_splits > 0 && ov.stream_k < 0 &&
+          t_tile / sk_splits * 1.05 + kTwoPassUs >= std::max(t_tile, kEpilogueUs))
+        sk_splits = 0;
+    }
     stream_k = sk_splits > 0;
-    sk_first = p.num_tiles - rest;
   }
   const int sk_tiles = stream_k ? p.num_tiles - sk_first : 0;
   if (stream_k &&
@@ -559,6 +600,10 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
   p.stream_k = stream_k;
   p.sk_first_tile = stream_k ? sk_first : 0;
   p.sk_splits = stream_k ? sk_splits : 0;
+  // All tiles cut uniformly: nothing follows the cut tiles that could hide a closing sum inside
+  // the GEMM kernel, so the sums go to a second kernel that uses every SM (tuning key 11 = 0:
+  // the last contributor to arrive sums, as for a cut last wave).
+  p.two_pass = stream_k && sk_splits > 0 && sk_first == 0 && ov.tuning[11] != 0;
   if (stream_k) {
     if (sk_splits > 0) {
       p.max_contrib = sk_splits;
@@ -692,6 +737,33 @@ int launch(DeviceState* st, const Plan& plan, const CUtensorMap& mx, const CUten
   return NEOGEMM_OK;
 }
 
+// Second pass of a two-pass split-K launch (see splitk_reduce_kernel): right behind the GEMM
+// kernel on the same stream, with the same set-up overlap.
+int launch_reduce(const DeviceState* st, const Plan& plan, const GemmParams& params,
+                  cudaStream_t stream, bool overlap_setup = true) {
+  const int tile_m = 128 * plan.cta_group;
+  const long long items = static_cast<long long>(plan.num_tiles) * tile_m * (plan.block_n / 8);
+  const long long blocks = std::min<long long>((items + 255) / 256, 8ll * st->sm_count);
+  cudaLaunchConfig_t cfg;
+  std::memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(static_cast<unsigned>(std::max<long long>(1, blocks)), 1, 1);
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = overlap_setup ? 1 : 0;
+  int tm = tile_m, bn = plan.block_n;
+  void* args[3] = {const_cast<GemmParams*>(&params), &tm, &bn};
+  if (cudaLaunchKernelExC(&cfg, reinterpret_cast<const void*>(&splitk_reduce_kernel), args) !=
+      cudaSuccess) {
+    cudaGetLastError();
+    return NEOGEMM_ERR_LAUNCH;
+  }
+  return NEOGEMM_OK;
+}
+
 // Optional fused epilogue: C = act(alpha * A B^T + beta * C + bias).
 struct Fusion {
   bool on = false;
@@ -794,6 +866,7 @@ int gemm_device(const void* A, const void* B, void* C, int64_t M, int64_t N, int
   params.dyn_piece_kb = plan.dyn_piece_kb;
   params.dyn_static_kb = plan.dyn_static_kb;
   params.max_contrib = plan.max_contrib;
+  params.sk_two_pass = plan.two_pass ? 1 : 0;
   params.status = st->status_dev;
   // Tuning key 8: wave pacing -1 auto (many waves of whole tiles), 0 off, 1 whenever applicable.
   {
@@ -867,7 +940,10 @@ int gemm_device(const void* A, const void* B, void* C, int64_t M, int64_t N, int
   t_last_config[7] = plan.group_m;
 
   std::lock_guard<std::mutex> lock(g_mu);  // attr_done bookkeeping
-  return launch(st, plan, mx, my, md, params, stream, t_override.tuning[10] != 0);
+  rc = launch(st, plan, mx, my, md, params, stream, t_override.tuning[10] != 0);
+  if (rc == NEOGEMM_OK && plan.two_pass)
+    rc = launch_reduce(st, plan, params, stream, t_override.tuning[10] != 0);
+  return rc;
 }
 
 int ensure_copy_queues(DeviceState* st) {
@@ -1144,7 +1220,7 @@ int neogemm_set_phase_timers(void* device_buffer, size_t bytes) {
 }
 
 int neogemm_set_tuning(int key, int value) {
-  if (key < 0 || key > 10 || (key == 6 && (value == 0 || value > 3)) || (key >= 8 && value > 1) || (key == 7 && value > 2) || (key == 5 && value > 3) || value > 1000000 || (key == 0 && value > 31) || (key == 3 && value > 1) ||
+  if (key < 0 || key > 11 || (key == 6 && (value == 0 || value > 3)) || (key >= 8 && value > 1) || (key == 7 && value > 2) || (key == 5 && value > 3) || value > 1000000 || (key == 0 && value > 31) || (key == 3 && value > 1) ||
       (key == 4 && value > 4))
     return NEOGEMM_ERR_BAD_ARG;
   t_override.tuning[key] = value;
@@ -1528,6 +1604,7 @@ int neogemm_bf16_nt_noalloc(const void* A, const void* B, void* C, int64_t M, in
   params.dyn_piece_kb = plan.dyn_piece_kb;
   params.dyn_static_kb = plan.dyn_static_kb;
   params.max_contrib = plan.max_contrib;
+  params.sk_two_pass = plan.two_pass ? 1 : 0;
   params.status = st->status;
   params.timers = nullptr;
   // Same K-direction rule as the regular entry point, so that both give the same bits.
@@ -1554,7 +1631,9 @@ int neogemm_bf16_nt_noalloc(const void* A, const void* B, void* C, int64_t M, in
   t_last_config[5] = plan.num_ctas;
   t_last_config[6] = plan.num_tiles;
   t_last_config[7] = plan.group_m;
-  return launch(&st->launch_state, plan, mx, my, md, params, stream);
+  rc = launch(&st->launch_state, plan, mx, my, md, params, stream);
+  if (rc == NEOGEMM_OK && plan.two_pass) rc = launch_reduce(&st->launch_state, plan, params, stream);
+  return rc;
 }
 
 }  // extern "C"

@@ -210,7 +210,8 @@ def set_override(cta_group: int = -1, block_n: int = -1, swap: int = -1, stream_
 TUNING_KEYS = {"l2_hints": 0, "epilogue_wait_hint_ns": 1, "ring_wait_hint_ns": 2, "wide_tile": 3,
                "dynamic_pieces_per_tile": 4, "l2_promotion": 5, "wide_tile_prologue": 6,
                "two_ctas_per_sm": 7, "wave_pacing": 8,
-               "k_direction_alternates": 9, "setup_overlap": 10}
+               "k_direction_alternates": 9, "setup_overlap": 10,
+               "two_pass_split_k": 11}
 
 
 def set_tuning(key: str, value: int = -1) -> None:

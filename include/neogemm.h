@@ -234,6 +234,11 @@ int neogemm_set_override(int cta_group, int block_n, int swap, int stream_k, int
  *          a launch's CTAs are placed and initialise barriers and tensor memory while the previous
  *          kernel of the stream drains; the kernel still waits for that kernel's completion before
  *          it touches global memory.  1 or -1 on, 0 off (plain stream order).
+ *   key 11: two-pass split-K.  When a launch has fewer tiles than SMs (or SM pairs) and K is
+ *          long, every tile is cut into 2..8 equal k-chunks, one per CTA; -1 or 1: the GEMM kernel
+ *          only publishes fp32 partials and a reduction kernel launched right behind it sums
+ *          them, applies the epilogue and stores C; 0: wide tiles are not cut at all and the
+ *          last contributor of a cut narrow tile sums it alone (the earlier behaviour).
  * No counterpart in the reference (its maps only set L2 promotion, nemgemmV03.cu:52). */
 int neogemm_set_tuning(int key, int value);
 

@@ -28,7 +28,7 @@ def reference(A, B, alpha, beta, c_old, bias, activation):
 CASES = [  # (M, N, K): pair kernel, cut last wave, single-CTA TMA store, direct, swapped stream-K,
     # whole tiles two CTAs to an SM
     (2048, 2048, 512), (4096, 4096, 1024), (520, 776, 264), (257, 250, 128), (16, 3584, 2048),
-    (64, 28672, 1024), (24, 20000, 1024),
+    (64, 28672, 1024), (24, 20000, 1024), (1024, 1024, 4096),   # the last: two-pass split-K
 ]
 
 
@@ -102,7 +102,7 @@ def assert_fp32_result(out, want, what):
 F32_CASES = [  # pair TMA-store, cut last wave, single-CTA TMA store, ragged edges with TMA store,
     # direct (N % 4 != 0), swapped stream-K, swapped whole tiles two CTAs to an SM, data-parallel
     (2048, 2048, 512), (4096, 4096, 1024), (520, 776, 264), (1000, 1004, 520), (257, 250, 128),
-    (16, 3584, 2048), (64, 28672, 1024), (1024, 768, 512),
+    (16, 3584, 2048), (64, 28672, 1024), (1024, 768, 512), (1024, 1024, 4096),
 ]
 
 

@@ -369,6 +369,34 @@ def test_bounded_wait_expires_into_an_error_code_and_the_library_recovers():
 
 @pytest.mark.parametrize("shape", [(512, 512, 8192), (256, 256, 4096), (300, 520, 4104)])
 def test_handful_of_tiles_under_long_k(shape):
-    stats, cfg = run_case(*shape)
+    # with the two-pass split-K switched off: 64-column direct-store tiles, last arriver sums
+    stats, cfg = run_case(*shape, tuning={"two_pass_split_k": 0})
     assert (cfg["block_n"], cfg["stream_k"]) == (64, 1), cfg
+    run_case(*shape, col_major=True, tuning={"two_pass_split_k": 0})
+
+
+@pytest.mark.parametrize("shape", [(1024, 1024, 8192), (512, 512, 8192), (256, 256, 4096),
+                                   (300, 520, 4104), (1536, 1024, 3072), (1000, 1016, 2056),
+                                   (640, 2048, 4096)])
+def test_two_pass_split_k(shape):
+    # Few wide tiles under a long K: every tile cut into k-chunks, partials summed, rounded and
+    # stored by the reduction kernel behind the GEMM.  Ragged edges, both layouts, and the same
+    # bits launch after launch.
+    stats, cfg = run_case(*shape)
+    picked = shape in ((1024, 1024, 8192), (512, 512, 8192), (256, 256, 4096), (300, 520, 4104))
+    if picked:   # the launcher cuts these on its own; the others only where forced below
+        assert cfg["stream_k"] == 1 and cfg["ctas"] > cfg["tiles"] * cfg["cta_group"], cfg
     run_case(*shape, col_major=True)
+    A, B = make_problem(*shape, seed=9)
+    dA, dB = A.cuda(), B.cuda()
+    first = ops.matmul(dA, dB).clone()
+    for _ in range(4):
+        assert torch.equal(first.view(torch.int16), ops.matmul(dA, dB).view(torch.int16))
+    # forced for every TMA-store kernel family
+    for ov in (dict(cta_group=1, block_n=256), dict(cta_group=1, block_n=128),
+               dict(cta_group=2, block_n=128), dict(cta_group=2, block_n=256)):
+        stats, cfg = run_case(*shape, override=dict(stream_k=1, **ov))
+        if cfg["tiles"] * 2 <= 148 // cfg["cta_group"] and shape[2] >= 1024:
+            assert cfg["stream_k"] == 1, cfg
+    torch.cuda.synchronize()
+    assert ops.device_status()[0] == 0

@@ -244,12 +244,27 @@ def test_hybrid_schedules_cover_the_problem(shape, override):
     check_cover(p, segs)
 
 
-def test_handful_of_tiles_under_long_k_is_cut_into_k_chunks():
-    # 512 x 512 x 8192: 64-column direct-store tiles, every tile cut, one chunk per CTA.
+def test_few_tiles_under_long_k_are_cut_into_k_chunks():
+    # Fewer tiles than workers and a long K: every tile in equal k-chunks, one per CTA, to be
+    # summed by the reduction kernel behind the launch (the TMA-store kernels' wide tiles).
+    p, segs = plan(1024, 1024, 8192)
+    assert (p["epi"], p["cta_group"], p["block_n"], p["stream_k"]) == (0, 2, 256, 1)
+    assert (p["tiles"], p["ctas"], p["max_contrib"], p["sk_first"]) == (16, 128, 4, 0)
+    check_cover(p, segs)
+    assert {(s[2], s[3]) for s in segs} == {(0, 32), (32, 32), (64, 32), (96, 32)}
     p, segs = plan(512, 512, 8192)
+    assert (p["epi"], p["stream_k"], p["tiles"], p["ctas"], p["max_contrib"]) == (0, 1, 16, 128, 8)
+    check_cover(p, segs)
+    # not where the second pass costs more than the shorter main loop saves, nor with whole waves
+    assert plan(1024, 1024, 1024)[0]["stream_k"] == 0
+    assert plan(512, 512, 512)[0]["stream_k"] == 0
+    assert plan(2048, 2048, 2048)[0]["stream_k"] == 0
+    # two-pass switched off: the earlier plans - wide tiles whole, and for a handful of tiles
+    # 64-column direct-store tiles whose last contributor sums
+    p, segs = plan(512, 512, 8192, tuning={11: 0})
     assert (p["epi"], p["block_n"], p["stream_k"], p["cta_group"]) == (1, 64, 1, 1)
     assert p["tiles"] == 32 and p["ctas"] == 128
     check_cover(p, segs)
-    # not with short K, nor with more 128 x 128 tiles than an eighth of the SMs
-    assert plan(512, 512, 2048)[0]["epi"] == 0
-    assert plan(1024, 1024, 8192)[0]["epi"] == 0
+    assert plan(512, 512, 2048, tuning={11: 0})[0]["epi"] == 0
+    p, segs = plan(1024, 1024, 8192, tuning={11: 0})
+    assert (p["epi"], p["stream_k"]) == (0, 0)
