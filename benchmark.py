@@ -59,7 +59,10 @@ def main():
     print(torch_result[:3, :3])
 
     neoGEMM.neoGemmV1(tensorA, tensorB, tensorC)
-    result = tensorC.t()            # the kernel writes column-major, as the reference does
+    # The kernel writes column-major, as the reference does: C's storage holds [N, M] row-major.
+    # For square sizes this is the reference's tensorC.t() (benchmark.py:25); reading the storage
+    # as [N, M] first makes the same view right for M != N too.
+    result = tensorC.view(N, M).t()
     print(f"2. neoGEMM.neoGemmV1: shape {tuple(result.shape)}, dtype {result.dtype}")
     print(result[:3, :3])
 

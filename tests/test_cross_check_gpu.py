@@ -157,3 +157,18 @@ def test_cpp_verify_and_timing_tool_builds_and_agrees():
         assert ", 0 outside rtol" in run.stdout, run.stdout
         assert "Divergence" not in run.stdout
         assert "phase timers over" in run.stdout
+
+
+@pytest.mark.timeout(300)
+def test_reference_style_driver_script_runs_and_agrees():
+    """benchmark.py, the counterpart of the reference's driver (benchmark.py:10-25,33-53,63-100):
+    builds operands, calls neoGEMM.neoGemmV1 through the torch extension, compares with torch's
+    matmul on the GPU and times both.  Run as the reference's users run it."""
+    pytest.importorskip("neoGEMM")
+    import sys
+    for args in (["--iters", "5"], ["--m", "520", "--n", "776", "--k", "264", "--scaled", "--iters", "2"]):
+        run = subprocess.run([sys.executable, os.path.join(ROOT, "benchmark.py"), *args],
+                             capture_output=True, text=True, timeout=240, cwd=ROOT)
+        assert run.returncode == 0, run.stdout[-2000:] + run.stderr[-2000:]
+        assert "tolerance 1e-02: PASS" in run.stdout, run.stdout
+        assert "neoGEMM:" in run.stdout and "TFLOPS" in run.stdout
