@@ -66,16 +66,11 @@ def sharded_matmul(A_block: torch.Tensor, B: Optional[torch.Tensor], N: int, K: 
 
 
 def sharded_matmul_overlapped(A_block: torch.Tensor, B: Optional[torch.Tensor], N: int, K: int,
-                              chunks: Optional[int] = None, group=None, src: int = 0,
+                              chunks: int = 4, group=None, src: int = 0,
                               matmul_out: Optional[Callable] = None):
-    """Same product with the broadcast of B hidden under compute: B travels in row blocks on a
-    side stream, and the product for the columns of C that a block feeds is launched as soon as
-    that block has landed in local HBM.  The kernel still reads local memory only.
-
-    ``chunks`` = None (default): three blocks of 1/8, 3/8 and 1/2 of B's rows - the first product
-    can start after an eighth of the broadcast, each product is long enough to cover the next,
-    larger block's transfer, and the product is cut into as few launches as that allows.  An
-    integer asks for that many equal blocks.
+    """Same product with the broadcast of B hidden under compute: B travels in ``chunks`` row
+    blocks on a side stream, and the product for the columns of C that a block feeds is launched
+    as soon as that block has landed in local HBM.  The kernel still reads local memory only.
 
     Returns (C_block, B_local).  ``matmul_out(A, B_rows, out)`` defaults to the CUDA operator
     writing into a column slice of C (row pitch N); CPU tests inject a stand-in."""
@@ -93,14 +88,10 @@ def sharded_matmul_overlapped(A_block: torch.Tensor, B: Optional[torch.Tensor], 
     else:
         B_local = torch.empty((N, K), dtype=A_block.dtype, device=A_block.device)
     C_block = torch.empty((A_block.shape[0], N), dtype=A_block.dtype, device=A_block.device)
-    # Column blocks on multiples of 512 / 256 (whole tiles) so that every launch sees whole tiles.
-    if chunks is None:
-        cuts = sorted({min(N, (N // 8 + 511) // 512 * 512), min(N, (N // 2 + 511) // 512 * 512), N})
-        bounds = [(a, b) for a, b in zip([0] + cuts[:-1], cuts) if b > a]
-    else:
-        chunks = max(1, min(chunks, (N + 255) // 256))
-        per = ((N + chunks - 1) // chunks + 255) // 256 * 256
-        bounds = [(n0, min(n0 + per, N)) for n0 in range(0, N, per)]
+    # Column blocks on multiples of 256 (one tile) so that every launch sees whole tiles.
+    chunks = max(1, min(chunks, (N + 255) // 256))
+    per = ((N + chunks - 1) // chunks + 255) // 256 * 256
+    bounds = [(n0, min(n0 + per, N)) for n0 in range(0, N, per)]
     on_gpu = A_block.is_cuda
     if on_gpu:
         compute = torch.cuda.current_stream(A_block.device)
