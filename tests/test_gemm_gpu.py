@@ -400,3 +400,45 @@ def test_two_pass_split_k(shape):
             assert cfg["stream_k"] == 1, cfg
     torch.cuda.synchronize()
     assert ops.device_status()[0] == 0
+
+
+def test_cuda_graph_replays_of_every_launch_kind():
+    # A captured graph of back-to-back launches (data-parallel, cut last wave, two-pass split-K
+    # with its reduction kernel, tall tiles, stream-K) where each launch's set-up overlaps the
+    # previous kernel's tail: replays must give the oracle's result every time, and a chained
+    # pair (the second product reads the first one's output) must see complete data.
+    shapes = [(1024, 768, 512), (4096, 4096, 1024), (1024, 1024, 4096), (48, 20000, 1024),
+              (16, 3584, 2048)]
+    problems = [make_problem(*s, seed=30 + i) for i, s in enumerate(shapes)]
+    dev = [(a.cuda(), b.cuda()) for a, b in problems]
+    outs = [torch.empty((s[0], s[1]), dtype=torch.bfloat16, device="cuda") for s in shapes]
+    # chain: D = (A0 B0^T) W^T with W [256, 768]
+    W = (torch.randn(256, 768, generator=torch.Generator().manual_seed(5)) / 768 ** 0.5) \
+        .to(torch.bfloat16)
+    dW = W.cuda()
+    chained = torch.empty((1024, 256), dtype=torch.bfloat16, device="cuda")
+
+    def launches():
+        for (dA, dB), out in zip(dev, outs):
+            ops.matmul(dA, dB, out=out)
+        ops.matmul(outs[0], dW, out=chained)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        launches()                       # workspace, attributes, tensor maps: before the capture
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        launches()
+    for replay in range(3):
+        for out in outs:
+            out.fill_(float("nan"))
+        chained.fill_(float("nan"))
+        graph.replay()
+        torch.cuda.synchronize()
+        assert ops.device_status()[0] == 0
+        for s, (A, B), out in zip(shapes, problems, outs):
+            oracle.assert_parity(out, oracle.gemm_fp32(A, B), f"graph replay {replay} {s}")
+        oracle.assert_parity(chained, oracle.gemm_fp32(outs[0].cpu(), W),
+                             f"chained product, replay {replay}")
