@@ -100,6 +100,7 @@ const KernelEntry* kernel_table(int* count) {
   static const KernelEntry table[] = {
       make_entry<GemmConfig<1, 256, 4, kEpiTmaStore>>(),
       make_entry<GemmConfig<1, 128, 6, kEpiTmaStore>>(),
+      make_entry<GemmConfig<1, 64, 8, kEpiTmaStore>>(),    // small problems: twice the CTAs
       make_entry<GemmConfig<2, 256, 4, kEpiTmaStore, 2>>(),   // 256 x 512 tile, both accumulators
       make_entry<GemmConfig<2, 256, 6, kEpiTmaStore>>(),
       make_entry<GemmConfig<2, 128, 8, kEpiTmaStore>>(),
@@ -173,7 +174,7 @@ bool g_encode_looked_up = false;
 
 struct Override {
   int cta_group = -1, block_n = -1, swap = -1, stream_k = -1, group_m = -1, max_ctas = -1;
-  int tuning[12] = {-1, -1, -1, -1, -1, -1, -1, -1, -1, -1, -1, -1};   // see neogemm_set_tuning
+  int tuning[13] = {-1, -1, -1, -1, -1, -1, -1, -1, -1, -1, -1, -1, -1};   // see neogemm_set_tuning
 };
 thread_local Override t_override;
 thread_local int t_last_config[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -448,7 +449,9 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
       const double t_main = 2.0 * static_cast<double>(tm) * static_cast<double>(tile_n) *
                             static_cast<double>(K) / (c.speed * 1e6 / workers_full);
       const double t_tile = (c.halves == 2) ? t_main + kHandOverUs : std::max(t_main, kEpilogueUs);
-      const double cost = waves * t_tile + extra_us;
+      // (the last term only breaks ties between kernels whose main loops all hide behind one
+      // epilogue: tiny problems take the kernel with the least work per CTA)
+      const double cost = waves * t_tile + extra_us + 0.01 * t_main;
       if (best == 0.0 || cost < best) {
         best = cost;
         best_group = c.cta_group;
@@ -459,6 +462,16 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
     cta_group = best_group;
     block_n = best_n;
     p.halves = best_halves;
+    // Small problems: when the 128 x 128 tiles would leave at least half of the SMs idle, 128 x 64
+    // tiles put twice as many to work.  Such launches are bound by the latency of the loads, not
+    // by the tensor pipe (about 1.3 us from issue to landing even out of L2): the narrower tile
+    // has a deeper ring (8 slots of 24 KB), half the MMA work and half the epilogue per CTA.
+    // Tuning key 12: -1 as described, 0 never, 1 whenever the 128 x 128 kernel would be used.
+    if (cta_group == 1 && block_n == 128 && p.halves == 1 && ov.block_n <= 0 && ov.tuning[12] != 0) {
+      const int64_t tiles128 = ((md + 127) / 128) * ((nd + 127) / 128);
+      // (up to K = 2048: few tiles under a longer K are cut into k-chunks instead, below)
+      if (ov.tuning[12] == 1 || (2 * tiles128 <= sm_count && (K + 63) / 64 <= 32)) block_n = 64;
+    }
   }
   p.block_n = block_n;
   p.cta_group = cta_group;
@@ -582,7 +595,7 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
       sk_splits = hybrid_splits(p.num_tiles, workers, p.num_k_blocks, 8);
       sk_first = 0;
       const double speed = cta_group == 2 ? (block_n == 256 ? 1570.0 : 975.0)
-                                          : (block_n == 256 ? 1430.0 : 1170.0);
+                                          : (block_n == 256 ? 1430.0 : block_n == 128 ? 1170.0 : 600.0);
       const double t_tile = 2.0 * tile_m * static_cast<double>(block_n) * static_cast<double>(K) /
                             (speed * 1e6 / std::max(1, sm_count / cta_group));
       if (sk_splits > 0 && ov.stream_k < 0 &&
@@ -1220,7 +1233,7 @@ int neogemm_set_phase_timers(void* device_buffer, size_t bytes) {
 }
 
 int neogemm_set_tuning(int key, int value) {
-  if (key < 0 || key > 11 || (key == 6 && (value == 0 || value > 3)) || (key >= 8 && value > 1) || (key == 7 && value > 2) || (key == 5 && value > 3) || value > 1000000 || (key == 0 && value > 31) || (key == 3 && value > 1) ||
+  if (key < 0 || key > 12 || (key == 6 && (value == 0 || value > 3)) || (key >= 8 && value > 1) || (key == 7 && value > 2) || (key == 5 && value > 3) || value > 1000000 || (key == 0 && value > 31) || (key == 3 && value > 1) ||
       (key == 4 && value > 4))
     return NEOGEMM_ERR_BAD_ARG;
   t_override.tuning[key] = value;

@@ -211,7 +211,7 @@ TUNING_KEYS = {"l2_hints": 0, "epilogue_wait_hint_ns": 1, "ring_wait_hint_ns": 2
                "dynamic_pieces_per_tile": 4, "l2_promotion": 5, "wide_tile_prologue": 6,
                "two_ctas_per_sm": 7, "wave_pacing": 8,
                "k_direction_alternates": 9, "setup_overlap": 10,
-               "two_pass_split_k": 11}
+               "two_pass_split_k": 11, "narrow_tiles": 12}
 
 
 def set_tuning(key: str, value: int = -1) -> None:

@@ -239,6 +239,9 @@ int neogemm_set_override(int cta_group, int block_n, int swap, int stream_k, int
  *          only publishes fp32 partials and a reduction kernel launched right behind it sums
  *          them, applies the epilogue and stores C; 0: wide tiles are not cut at all and the
  *          last contributor of a cut narrow tile sums it alone (the earlier behaviour).
+ *   key 12: 128 x 64 tiles for small problems (twice as many CTAs as 128 x 128 tiles): -1 when
+ *          the 128 x 128 tiles would occupy at most half of the SMs, 0 never, 1 whenever the
+ *          single-CTA 128 x 128 TMA-store kernel would be used.
  * No counterpart in the reference (its maps only set L2 promotion, nemgemmV03.cu:52). */
 int neogemm_set_tuning(int key, int value);
 

@@ -134,14 +134,20 @@ def test_wave_pacing_changes_neither_bits_nor_much_time(shape):
     A, B = make_problem(*shape, seed=21)
     dA, dB = A.cuda(), B.cuda()
 
+    out_buf = torch.empty((shape[0], shape[1]), dtype=torch.bfloat16, device="cuda")
+
     def timed(n):
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
+        # every launch between its own pair of events; the median, so that one stall of the
+        # machine (another process, a clock change) does not decide the comparison
+        times = []
         for _ in range(n):
-            out = ops.matmul(dA, dB)
-        e1.record()
-        e1.synchronize()
-        return out, e0.elapsed_time(e1) / n
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            out = ops.matmul(dA, dB, out=out_buf)
+            e1.record()
+            e1.synchronize()
+            times.append(e0.elapsed_time(e1))
+        return out.clone(), sorted(times)[len(times) // 2]
 
     ops.set_tuning("wave_pacing", 0)
     try:
