@@ -86,10 +86,6 @@ struct GemmParams {
                              // one per worker (worker w takes chunk w / tiles of tile w % tiles),
                              // instead of one contiguous unit range per worker
   int max_contrib;           // partial slots per tile in `partials`
-  int sk_two_pass;           // 1: contributors of a cut tile only publish their partials; the
-                             // closing sums, the epilogue arithmetic and the stores of those
-                             // tiles are done by splitk_reduce_kernel, launched right behind
-                             // this kernel.  0: the last contributor to arrive finishes the tile.
   // Dynamic tail pool (pure stream-K only; all zero otherwise).  The last dyn_ppt * dyn_piece_kb
   // k-blocks of every tile are not part of any CTA's static range: they form dyn_pieces fixed
   // pieces that CTAs claim from `dyn_counter` as they run out of static work, which evens out
@@ -114,6 +110,10 @@ struct GemmParams {
   long long* timers;
   // Error reporting: status[0] = code, [1] = blockIdx, [2] = segment index, [3] = stage / acc.
   int* status;
+  int sk_two_pass;           // 1: contributors of a cut tile only publish their partials; the
+                             // closing sums, the epilogue arithmetic and the stores of those
+                             // tiles are done by splitk_reduce_kernel, launched right behind
+                             // this kernel.  0: the last contributor to arrive finishes the tile.
 };
 
 template <int kCtaGroup_, int BLOCK_N_, int kStages_, int kEpiMode_, int kNHalves_ = 1,

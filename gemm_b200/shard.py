@@ -67,13 +67,17 @@ def sharded_matmul(A_block: torch.Tensor, B: Optional[torch.Tensor], N: int, K: 
 
 def sharded_matmul_overlapped(A_block: torch.Tensor, B: Optional[torch.Tensor], N: int, K: int,
                               chunks: int = 4, group=None, src: int = 0,
-                              matmul_out: Optional[Callable] = None):
+                              matmul_out: Optional[Callable] = None,
+                              out: Optional[torch.Tensor] = None,
+                              B_buffer: Optional[torch.Tensor] = None):
     """Same product with the broadcast of B hidden under compute: B travels in ``chunks`` row
     blocks on a side stream, and the product for the columns of C that a block feeds is launched
     as soon as that block has landed in local HBM.  The kernel still reads local memory only.
 
     Returns (C_block, B_local).  ``matmul_out(A, B_rows, out)`` defaults to the CUDA operator
-    writing into a column slice of C (row pitch N); CPU tests inject a stand-in."""
+    writing into a column slice of C (row pitch N); CPU tests inject a stand-in.  ``out`` ([rows,
+    N]) and ``B_buffer`` ([N, K], used on the receiving ranks) let a caller that repeats the
+    product keep its buffers instead of allocating them per call."""
     import torch.distributed as dist
     if matmul_out is None:
         from .ops import matmul as _mm
@@ -85,9 +89,18 @@ def sharded_matmul_overlapped(A_block: torch.Tensor, B: Optional[torch.Tensor], 
         if B is None or tuple(B.shape) != (N, K):
             raise ValueError(f"rank {src} must supply B with shape [{N},{K}]")
         B_local = B
+    elif B_buffer is not None:
+        if tuple(B_buffer.shape) != (N, K):
+            raise ValueError(f"B_buffer must have shape [{N},{K}]")
+        B_local = B_buffer
     else:
         B_local = torch.empty((N, K), dtype=A_block.dtype, device=A_block.device)
-    C_block = torch.empty((A_block.shape[0], N), dtype=A_block.dtype, device=A_block.device)
+    if out is not None:
+        if tuple(out.shape) != (A_block.shape[0], N):
+            raise ValueError(f"out must have shape [{A_block.shape[0]},{N}]")
+        C_block = out
+    else:
+        C_block = torch.empty((A_block.shape[0], N), dtype=A_block.dtype, device=A_block.device)
     # Column blocks on multiples of 256 (one tile) so that every launch sees whole tiles.
     chunks = max(1, min(chunks, (N + 255) // 256))
     per = ((N + chunks - 1) // chunks + 255) // 256 * 256

@@ -108,6 +108,15 @@ def _worker_overlap(rank, world, port, M, N, K, out_dir):
         assert torch.equal(B_local.view(torch.int16), B.view(torch.int16))
         want = oracle.gemm_bf16(A, B)[r0:r1]
         assert torch.equal(C_block.view(torch.int16), want.contiguous().view(torch.int16))
+        # with the caller's buffers
+        keep_c = torch.full((r1 - r0, N), float("nan"), dtype=torch.bfloat16)
+        keep_b = B.clone() if rank == 0 else torch.zeros((N, K), dtype=torch.bfloat16)
+        C2, B2 = sharded_matmul_overlapped(A[r0:r1].contiguous(), keep_b if rank == 0 else None, N, K,
+                                           chunks=2, matmul_out=stand_in, out=keep_c,
+                                           B_buffer=keep_b)
+        assert C2 is keep_c and (rank == 0 or B2 is keep_b)
+        assert torch.equal(keep_b.view(torch.int16), B.view(torch.int16))
+        assert torch.equal(keep_c.view(torch.int16), want.contiguous().view(torch.int16))
         open(os.path.join(out_dir, f"ok{rank}"), "w").close()
     finally:
         dist.destroy_process_group()
