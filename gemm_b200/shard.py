@@ -226,12 +226,16 @@ class ShardedHostPipeline:
                 ev.record(self.s_in)
                 ups.append(ev)
         cur.wait_event(b_ready)
-        for (r0, r1), up in zip(self.a_bounds, ups):
+        for i, ((r0, r1), up) in enumerate(zip(self.a_bounds, ups)):
             cur.wait_event(up)
             self.matmul_out(self.dA[r0:r1], self.dB, self.dC[r0:r1])
             done = torch.cuda.Event()
             done.record(cur)
             self.s_out.wait_event(done)
+            # Downloads start on upload boundaries (a download that starts in the middle of an
+            # upload slows it by more than the wait costs: measured on the single-GPU entry point).
+            if i + 1 < len(ups):
+                self.s_out.wait_event(ups[i + 1])
             with torch.cuda.stream(self.s_out):
                 hC_block[r0:r1].copy_(self.dC[r0:r1], non_blocking=True)
         cur.wait_stream(self.s_out)
