@@ -58,6 +58,10 @@ struct GemmParams {
   int l2_hints;              // bit 0: X loads evict-last, bit 1: Y loads evict-first,
                              // bit 2: D stores evict-first, bit 3: X loads evict-first,
                              // bit 4: Y loads evict-last (0 = no hints)
+                             // bit 5 (set by the launcher, not a hint): a tall tile stores its
+                             // transposed bf16 result through the TMA unit, tmap_d is its map
+                             // bit 6 (set by the launcher): the same with the operands' roles
+                             // exchanged in the MMA (GemmConfig::kFlippable)
   int epi_wait_hint_ns;      // suspend hint of the epilogue's wait for an accumulator (0 = none)
   int main_wait_hint_ns;     // suspend hint of the producer's and the MMA warp's ring waits
   int wide_prologue;         // two-half tiles: k-blocks issued for half 0 alone at a tile's start
@@ -132,6 +136,18 @@ struct GemmConfig {
   // takes half as much of every ring slot and the ring of the streamed operand gets deeper.
   static constexpr int kMHalves = kMHalves_;
   static constexpr int kTallRows = 208;
+  // A pair of tall tiles with 128 columns can run with the operands' roles exchanged in the MMA
+  // (a run-time choice, GemmParams::l2_hints bit 6).  As described above the pair issues two
+  // 256 x 128 instructions per k-step, the second for rows 128..255 of each CTA's tile of which
+  // only tile_rows - 128 exist: at 200 rows 22 % of the tensor work is spent on rows nobody
+  // stores, and under the power cap, where these shapes run at half the idle clock, the tensor
+  // pipe is the busiest unit of the SM.  Exchanged, the 2 x 64 rows of Y are the M side of a
+  // 128-row pair instruction and X's rows are its N side, which comes in steps of 16: one
+  // instruction of N = 256 (rows 0..127 of both CTAs' tiles) and one of N = 2 x (tile_rows -
+  // 128), nothing wasted.  The same bytes sit in the same shared memory; only the descriptors
+  // trade places.  The accumulator then is D transposed: lane l of a CTA holds row
+  // 64 x rank + (l mod 64) of Y against tile row j of the CTA l / 64 of the pair in column j.
+  static constexpr bool kFlippable = (kMHalves_ == 2 && kCtaGroup_ == 2 && BLOCK_N_ == 128);
   static constexpr int kCtaGroup = kCtaGroup_;
   static constexpr int BLOCK_N = BLOCK_N_;           // UMMA N
   // kNHalves == 2: the tile is two UMMA-N-wide halves side by side that share the X operand, each
@@ -166,7 +182,7 @@ struct GemmConfig {
   static constexpr int SMEM_EPI_T_WARP = kDirectCols * 64;
   static constexpr int SMEM_EPI = (kEpiMode == kEpiTmaStore) ? kEpiWarps * kEpiBufs * SMEM_EPI_WARP_BUF
                                                              : 4 * SMEM_EPI_T_WARP;
-  static constexpr int SMEM_BARRIERS = (2 * kStages + 8) * 8 + 16;
+  static constexpr int SMEM_BARRIERS = (2 * kStages + 9) * 8 + 16;
   // +1024: the ring must start on a 1024-byte boundary for the 128-byte swizzle.
   static constexpr int SMEM_TOTAL = kStages * SMEM_STAGE + SMEM_EPI + SMEM_BARRIERS + 1024;
   static constexpr int kAccumCols = BLOCK_N * kMHalves;   // fp32 columns per accumulator set
@@ -188,6 +204,8 @@ struct GemmConfig {
   static_assert(kCtaGroup == 1 || kTmemCols == 512,
                 "pair mode allocates all of tensor memory so both CTAs get column 0");
   static_assert(SMEM_TOTAL <= 232448, "exceeds 227 KB of shared memory per CTA");
+  static_assert(kMHalves == 1 || BLOCK_N * kTallRows * 2 <= kStages * SMEM_STAGE,
+                "a tall tile stages its whole result in the idle ring");
   static_assert(kMHalves == 1 || (kMHalves == 2 && kNHalves == 1 && kEpiMode == kEpiDirect &&
                                   2 * kAccumCols <= 512),
                 "two M-halves: direct-store kernels with both accumulator sets in TMEM");
@@ -605,7 +623,8 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
   const uint32_t tmem_empty_bar = tmem_full_bar + 16;       // [2]
   const uint32_t sched_full_bar = tmem_empty_bar + 16;      // [2] dynamic-claim queue
   const uint32_t sched_empty_bar = sched_full_bar + 16;     // [2]
-  const uint32_t tmem_slot = sched_empty_bar + 16;          // u32
+  const uint32_t epi_sync_bar = sched_empty_bar + 16;       // [1] tall tiles: result staged
+  const uint32_t tmem_slot = epi_sync_bar + 8;              // u32
   uint8_t* tail_gen = smem_gen + (tmem_slot - smem_base);
   volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(tail_gen);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tail_gen + 4);
@@ -635,12 +654,14 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
       mbar_init(sched_full_bar + 8 * a, 1);                   // the claiming lane
       mbar_init(sched_empty_bar + 8 * a, 1 + Cfg::kEpiWarps); // MMA warp + epilogue warps
     }
+    mbar_init(epi_sync_bar, 4);   // the four epilogue warps of a tall tile
     fence_barrier_init();
   }
   if (warp == 0 && lane == 0) {
     prefetch_tensormap(&tmap_x);
     prefetch_tensormap(&tmap_y);
-    if (Cfg::kEpiMode == kEpiTmaStore) prefetch_tensormap(&tmap_d);
+    if (Cfg::kEpiMode == kEpiTmaStore || (Cfg::kMHalves == 2 && (p.l2_hints & 32)))
+      prefetch_tensormap(&tmap_d);
   }
   if (warp == 1) {
     tmem_alloc<1>(tmem_slot, Cfg::kTmemCols);
@@ -762,6 +783,9 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
       uint32_t stage = 0, phase = 0;
       int seg_idx = 0;
       constexpr uint32_t idesc = make_idesc_bf16(Cfg::UMMA_M, BLOCK_N);
+      const uint32_t idesc_flip0 = make_idesc_bf16(128, 256);
+      const uint32_t idesc_flip1 =
+          make_idesc_bf16(128, static_cast<uint32_t>(2 * max(p.tile_rows - 128, 8)));
       bool ok = true;
       GemmParams timer_params = p;
       if (lane != 0) timer_params.timers = nullptr;
@@ -879,6 +903,19 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
 #pragma unroll
             for (int k = 0; k < Cfg::BLOCK_K / Cfg::UMMA_K; ++k) {
               // +32 bytes (two 16-byte units) per 16-element K step inside the swizzle row.
+              if constexpr (Cfg::kFlippable) {
+                if (p.l2_hints & 64) {
+                  // Roles exchanged (see kFlippable): Y's 2 x 64 rows are the M side, X's rows
+                  // the N side - 2 x 128 of them in the first instruction, the 2 x (tile_rows -
+                  // 128) below them in the second, whose columns follow in tensor memory.
+                  umma_bf16<kCtaGroup>(tmem_d, desc_y + 2 * k, desc_x + 2 * k, idesc_flip0,
+                                       (kb > 0 || k > 0) ? 1u : 0u);
+                  umma_bf16<kCtaGroup>(tmem_d + 128, desc_y + 2 * k,
+                                       desc_x + (Cfg::SMEM_X_HALF >> 4) + 2 * k, idesc_flip1,
+                                       (kb > 0 || k > 0) ? 1u : 0u);
+                  continue;
+                }
+              }
               if constexpr (Cfg::kMHalves == 2) {
                 // Two blocks of X rows, one Y: the second block sits SMEM_X_HALF further on.
 #pragma unroll
@@ -1304,9 +1341,112 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
           ++store_count;
         }
       } else {
+        bool stored = false;
+        if constexpr (Cfg::kFlippable) {
+          if (p.l2_hints & 64) {
+            // Exchanged roles (see kFlippable): this lane holds, for ONE row of Y, the tile rows
+            // 0 .. tile_rows-1 of one CTA of the pair in columns 0 .. tile_rows-1 - for a
+            // transposed result that is tile_rows x 2 contiguous bytes.  The lanes stage their
+            // rows in the idle ring as [half of the lanes][64 rows of Y][tile_rows], 16 bytes
+            // at a time, and one thread hands each half to the TMA unit as one box.
+            const int m_local = row_in_cta & 63;
+            const uint32_t owner = quad >> 1;
+            const uint32_t pitch = static_cast<uint32_t>(p.tile_rows) * 2u;
+            const uint32_t dst = ring + owner * (64u * pitch) + static_cast<uint32_t>(m_local) * pitch;
+#pragma unroll 1
+            for (int c = 0; c < p.tile_rows; c += 32) {
+              uint32_t r[32];
+              __syncwarp();
+              tmem_ld_32x32b_x32(taddr_tile + c, r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int v8 = 0; v8 < 4; ++v8) {
+                if (c + 8 * v8 < p.tile_rows)
+                  st_shared_v4(dst + static_cast<uint32_t>(c + 8 * v8) * 2u,
+                               pack_bf16x2(__uint_as_float(r[8 * v8 + 0]), __uint_as_float(r[8 * v8 + 1])),
+                               pack_bf16x2(__uint_as_float(r[8 * v8 + 2]), __uint_as_float(r[8 * v8 + 3])),
+                               pack_bf16x2(__uint_as_float(r[8 * v8 + 4]), __uint_as_float(r[8 * v8 + 5])),
+                               pack_bf16x2(__uint_as_float(r[8 * v8 + 6]), __uint_as_float(r[8 * v8 + 7])));
+              }
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(epi_sync_bar);
+            if (warp == 2 && lane == 0) {
+              if (mbar_wait(epi_sync_bar, static_cast<uint32_t>(seg_idx & 1), abort_flag)) {
+                const int y = col0 + static_cast<int>(cta_rank) * 64;
+#pragma unroll 1
+                for (int o = 0; o < 2; ++o) {
+                  const int x = (tm * 2 + o) * p.tile_rows;
+                  if (x < p.Md && y < p.Nd)
+                    tma_store_2d(&tmap_d, ring + static_cast<uint32_t>(o) * (64u * pitch), x, y);
+                }
+                tma_store_commit();
+              } else {
+                report_error(p, abort_flag, kDevTimeoutEpilogue, seg_idx, 7);
+              }
+            }
+            stored = true;
+          }
+        }
+        if constexpr (Cfg::kMHalves == 2) {
+          if (!stored && (p.l2_hints & 32)) {
+            // Tall tile with a transposed bf16 result (rows of D contiguous in memory), the
+            // decode case.  A tall tile is its CTA's only tile, so this walk is the exposed tail
+            // of the launch, and it is bound by SM cycles, not by memory: stores from registers
+            // took 700 cycles per 32-column step (four 16-byte store instructions, each eight
+            // 64-byte pieces of eight different lines) against 155 for staging the step and 23
+            // for reading it from tensor memory - the same count at any clock, and under the
+            // power cap these shapes run at half the idle clock.  So the tile goes out as ONE
+            // box: the operand ring is idle by now (every copy into it has been consumed by an
+            // MMA that has completed), the four warps stage the whole tile there as
+            // [column][tile_rows], a column being tile_rows x 2 contiguous bytes of the result,
+            // and one thread hands it to the TMA unit, which clips it at the matrix edge.
+            constexpr int kDC = Cfg::kDirectCols;
+            const uint32_t pitch = static_cast<uint32_t>(p.tile_rows) * 2u;
+#pragma unroll 1
+            for (int mh = 0; mh < 2; ++mh) {
+              const int r_in_tile = mh * Cfg::BLOCK_M + static_cast<int>(quad) * 32;
+              if (r_in_tile >= p.tile_rows) continue;               // (warp-uniform)
+              const bool mine = r_in_tile + static_cast<int>(lane) < p.tile_rows;
+              const uint32_t taddr = taddr_tile + static_cast<uint32_t>(mh) * BLOCK_N;
+              const uint32_t dst = ring + static_cast<uint32_t>(r_in_tile + static_cast<int>(lane)) * 2u;
+#pragma unroll 1
+              for (int c = 0; c < BLOCK_N; c += kDC) {
+                uint32_t r[kDC];
+                __syncwarp();
+                if constexpr (kDC == 32) tmem_ld_32x32b_x32(taddr + c, r);
+                else tmem_ld_32x32b_x16(taddr + c, r);
+                tmem_ld_wait();
+                if (p.fuse)
+                  fused_epilogue<kDC>(r, p, row0_tile + r_in_tile + static_cast<int>(lane), col0 + c);
+                if (mine) {
+#pragma unroll
+                  for (int j = 0; j < kDC; ++j)
+                    st_shared_b16(dst + static_cast<uint32_t>(c + j) * pitch,
+                                  __bfloat16_as_ushort(__float2bfloat16_rn(__uint_as_float(r[j]))));
+                }
+              }
+            }
+            // Writers fence their own writes towards the async proxy, then meet at a barrier of
+            // the four epilogue warps; only the issuing thread has to wait there (bounded).
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(epi_sync_bar);
+            if (warp == 2 && lane == 0) {
+              if (mbar_wait(epi_sync_bar, static_cast<uint32_t>(seg_idx & 1), abort_flag)) {
+                tma_store_2d(&tmap_d, ring, row0_tile, col0);
+                tma_store_commit();
+              } else {
+                report_error(p, abort_flag, kDevTimeoutEpilogue, seg_idx, 7);
+              }
+            }
+            stored = true;
+          }
+        }
         // Two M-halves: the same walk twice, 128 rows and BLOCK_N accumulator columns further on.
 #pragma unroll 1
-        for (int mh = 0; mh < Cfg::kMHalves; ++mh) {
+        for (int mh = 0; mh < (stored ? 0 : Cfg::kMHalves); ++mh) {
         const int row0 = row0_tile + mh * Cfg::BLOCK_M;
         const uint32_t taddr = taddr_tile + static_cast<uint32_t>(mh) * BLOCK_N;
         const int row = row0 + row_in_cta;
@@ -1441,7 +1581,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
     if (it.failed && lane == 0) report_error(p, abort_flag, kDevTimeoutScheduler, seg_idx, 2);
     // Shared memory must outlive the stores' reads of it; their writes to global memory are
     // complete when the grid is, which is all a later kernel or copy can observe.
-    if (Cfg::kEpiMode == kEpiTmaStore && lane == 0) tma_store_wait_read<0>();
+    if ((Cfg::kEpiMode == kEpiTmaStore || Cfg::kMHalves == 2) && lane == 0) tma_store_wait_read<0>();
     loop_timer.end();
     loop_timer.stamp(11);
     loop_timer.flush(6);

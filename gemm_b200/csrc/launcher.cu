@@ -267,7 +267,9 @@ constexpr size_t kMapCacheSize = 128;
 int get_tensor_map(const void* base, uint64_t inner, uint64_t rows, uint64_t pitch_bytes,
                    uint32_t box_rows, int for_store, CUtensorMap* out) {
   // for_store: 1 = store map (no promotion), 2 = store map of an fp32 matrix (`inner` fp32
-  // elements per row, box 32 x box_rows: again one 128-byte swizzle row); loads: 0 = 256-byte L2
+  // elements per row, box 32 x box_rows: again one 128-byte swizzle row), 1000 + n = store map
+  // with a box of n bf16 (a multiple of 8, at most 256) x box_rows, dense in shared memory (no
+  // swizzle): the transposed result of a tall tile; loads: 0 = 256-byte L2
   // promotion (default), -1 none, -2 64 B, -3 128 B (tuning key 5).
   const MapKey key{base, inner, rows, pitch_bytes, box_rows, for_store};
   for (size_t i = t_map_cache.size(); i-- > 0;) {
@@ -283,13 +285,16 @@ int get_tensor_map(const void* base, uint64_t inner, uint64_t rows, uint64_t pit
   }
   cuuint64_t dims[2] = {inner, rows};
   cuuint64_t strides[1] = {pitch_bytes};
-  cuuint32_t box[2] = {for_store == 2 ? 32u : 64u, box_rows};
+  cuuint32_t box[2] = {for_store >= 1000 ? static_cast<cuuint32_t>(for_store - 1000)
+                                         : for_store == 2 ? 32u : 64u, box_rows};
+  if (for_store >= 1000 && (for_store > 1256 || (for_store & 7) != 0)) return NEOGEMM_ERR_UNSUPPORTED;
   cuuint32_t elem_strides[2] = {1, 1};
   CUtensorMap m;
   const CUresult r = g_encode(
       &m, for_store == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
       const_cast<void*>(base), dims, strides, box,
-      elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+      elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+      for_store >= 1000 ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
       for_store >= 1 ? CU_TENSOR_MAP_L2_PROMOTION_NONE
       : for_store == -1 ? CU_TENSOR_MAP_L2_PROMOTION_NONE
       : for_store == -2 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
@@ -490,7 +495,8 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
   //  * 128-row tiles with two CTAs per SM and half-size rings, when there are at most two such
   //    tiles per SM and the tall tiles would have to be higher than 208 rows.
   // Tuning key 7: -1 as described, 0 neither (stream-K), 1 two CTAs per SM whenever the kernel
-  // exists and the tiles fit, 2 tall tiles for any row count up to 208 rows per SM.
+  // exists and the tiles fit, 2 tall tiles for any row count up to 208 rows per SM, 3 and 4 as
+  // -1 with another store path for tall tiles (see gemm_device).
   int mhalves = 1, tile_rows = 0;
   bool two_per_sm_auto = false;
   {
@@ -503,14 +509,15 @@ int make_plan(int64_t pm, int64_t pn, int64_t K, int64_t ldc, const void* C, int
                              ov.max_ctas <= 0 && (K + 63) / 64 >= 16;
     const bool tall_fits = rows <= 208 && ((md + rows - 1) / rows) * n_tiles <= sm_count;
     if (one_wave_ok && tall_fits &&
-        ((ov.tuning[7] < 0 && tiles128 > sm_count) || ov.tuning[7] == 2)) {
+        (((ov.tuning[7] < 0 || ov.tuning[7] >= 3) && tiles128 > sm_count) || ov.tuning[7] == 2)) {
       mhalves = 2;
       tile_rows = static_cast<int>(rows);
       // From 64 columns on the small operand is worth splitting between two CTAs: pairs of
       // tall tiles (2 x tile_rows rows per pair), provided the pairs still fit in one wave.
       const int64_t pair_tiles = ((md + 2 * rows - 1) / (2 * rows)) * n_tiles;
       if (block_n >= 64 && ov.cta_group != 1 && 2 * pair_tiles <= sm_count) cta_group = 2;
-    } else if (one_wave_ok && ov.tuning[7] < 0 && tiles128 > sm_count && tiles128 <= 2ll * sm_count) {
+    } else if (one_wave_ok && (ov.tuning[7] < 0 || ov.tuning[7] >= 3) && tiles128 > sm_count &&
+               tiles128 <= 2ll * sm_count) {
       two_per_sm_auto = true;
     }
   }
@@ -778,6 +785,15 @@ int launch_reduce(const DeviceState* st, const Plan& plan, const GemmParams& par
 }
 
 // Optional fused epilogue: C = act(alpha * A B^T + beta * C + bias).
+// A tall tile hands a transposed bf16 result (rows of D contiguous in memory: the operands were
+// swapped) to the TMA unit instead of storing it from registers; the map's box is the whole tile,
+// tile_rows rows of D (contiguous bytes) by the tile's columns.  Tile heights are multiples of 8,
+// so every box starts on a 16-byte boundary and its rows are whole 16-byte units.
+bool tall_tile_tma_store(const Plan& plan, const void* C, int64_t ldc, int c_elem) {
+  return plan.mhalves == 2 && plan.swap && c_elem == 2 && (ldc & 7) == 0 &&
+         (reinterpret_cast<uintptr_t>(C) & 15) == 0 && (plan.tile_rows & 7) == 0;
+}
+
 struct Fusion {
   bool on = false;
   float alpha = 1.f, beta = 0.f;
@@ -847,6 +863,18 @@ int gemm_device(const void* A, const void* B, void* C, int64_t M, int64_t N, int
                         static_cast<uint64_t>(ldc) * c_elem, 32, fusion.out_f32 ? 2 : 1, &md);
     if (rc != NEOGEMM_OK) return rc;
   }
+  // Tuning key 7 = 3: tall tiles as by default, but stored from registers; 4: stored through the
+  // TMA unit, but the pair kernel of 128 columns keeps the operands' usual roles.
+  const bool tall_tma = tall_tile_tma_store(plan, C, ldc, c_elem) && t_override.tuning[7] != 3;
+  const bool tall_flip = tall_tma && plan.cta_group == 2 && plan.block_n == 128 && !fusion.on &&
+                         t_override.tuning[7] != 4;
+  if (tall_tma) {
+    rc = get_tensor_map(C, static_cast<uint64_t>(plan.Md), static_cast<uint64_t>(plan.Nd),
+                        static_cast<uint64_t>(ldc) * 2,
+                        tall_flip ? 64u : static_cast<uint32_t>(plan.block_n),
+                        1000 + plan.tile_rows, &md);
+    if (rc != NEOGEMM_OK) return rc;
+  }
 
   GemmParams params;
   std::memset(&params, 0, sizeof(params));
@@ -864,7 +892,8 @@ int gemm_device(const void* A, const void* B, void* C, int64_t M, int64_t N, int
   // push Y and the stream-K partials out of L2 (measured: 5 % at M=16, 9 % at M=128 on the decode
   // shapes).
   const int default_hints = (plan.epi == kEpiDirect && plan.num_n_tiles == 1) ? 24 : kDefaultTuning[0];
-  params.l2_hints = t_override.tuning[0] >= 0 ? t_override.tuning[0] : default_hints;
+  params.l2_hints = (t_override.tuning[0] >= 0 ? t_override.tuning[0] : default_hints) |
+                    (tall_flip ? 64 : tall_tma ? 32 : 0);
   params.epi_wait_hint_ns = t_override.tuning[1] >= 0 ? t_override.tuning[1] : kDefaultTuning[1];
   params.main_wait_hint_ns = t_override.tuning[2] >= 0 ? t_override.tuning[2] : kDefaultTuning[2];
   params.wide_prologue = t_override.tuning[6] >= 0 ? t_override.tuning[6] : kDefaultWidePrologue;
@@ -1247,7 +1276,7 @@ int neogemm_set_phase_timers(void* device_buffer, size_t bytes) {
 }
 
 int neogemm_set_tuning(int key, int value) {
-  if (key < 0 || key > 12 || (key == 6 && (value == 0 || value > 3)) || (key >= 8 && value > 1) || (key == 7 && value > 2) || (key == 5 && value > 3) || value > 1000000 || (key == 0 && value > 31) || (key == 3 && value > 1) ||
+  if (key < 0 || key > 12 || (key == 6 && (value == 0 || value > 3)) || (key >= 8 && value > 1) || (key == 7 && value > 4) || (key == 5 && value > 3) || value > 1000000 || (key == 0 && value > 31) || (key == 3 && value > 1) ||
       (key == 4 && value > 4))
     return NEOGEMM_ERR_BAD_ARG;
   t_override.tuning[key] = value;
@@ -1447,11 +1476,13 @@ int encode_map_uncached(const void* base, uint64_t inner, uint64_t rows, uint64_
   }
   cuuint64_t dims[2] = {inner, rows};
   cuuint64_t strides[1] = {pitch_bytes};
-  cuuint32_t box[2] = {64, box_rows};
+  cuuint32_t box[2] = {for_store >= 1000 ? static_cast<cuuint32_t>(for_store - 1000) : 64u, box_rows};
+  if (for_store >= 1000 && (for_store > 1256 || (for_store & 7) != 0)) return NEOGEMM_ERR_UNSUPPORTED;
   cuuint32_t elem_strides[2] = {1, 1};
   const CUresult r = g_static_encode(
       out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
-      elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+      elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+      for_store >= 1000 ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
       for_store ? CU_TENSOR_MAP_L2_PROMOTION_NONE : CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? NEOGEMM_OK : NEOGEMM_ERR_DESCRIPTOR;
@@ -1603,6 +1634,15 @@ int neogemm_bf16_nt_noalloc(const void* A, const void* B, void* C, int64_t M, in
                              static_cast<uint64_t>(ldc) * 2, 32, 1, &md);
     if (rc != NEOGEMM_OK) return rc;
   }
+  const bool tall_tma = tall_tile_tma_store(plan, C, ldc, 2);
+  const bool tall_flip = tall_tma && plan.cta_group == 2 && plan.block_n == 128;
+  if (tall_tma) {
+    rc = encode_map_uncached(C, static_cast<uint64_t>(plan.Md), static_cast<uint64_t>(plan.Nd),
+                             static_cast<uint64_t>(ldc) * 2,
+                             tall_flip ? 64u : static_cast<uint32_t>(plan.block_n),
+                             1000 + plan.tile_rows, &md);
+    if (rc != NEOGEMM_OK) return rc;
+  }
 
   GemmParams params;
   std::memset(&params, 0, sizeof(params));
@@ -1615,7 +1655,8 @@ int neogemm_bf16_nt_noalloc(const void* A, const void* B, void* C, int64_t M, in
   params.num_k_blocks = plan.num_k_blocks;
   params.group_m = plan.group_m;
   params.tile_rows = plan.tile_rows;
-  params.l2_hints = (plan.epi == kEpiDirect && plan.num_n_tiles == 1) ? 24 : kDefaultTuning[0];
+  params.l2_hints = ((plan.epi == kEpiDirect && plan.num_n_tiles == 1) ? 24 : kDefaultTuning[0]) |
+                    (tall_flip ? 64 : tall_tma ? 32 : 0);
   params.epi_wait_hint_ns = kDefaultTuning[1];
   params.main_wait_hint_ns = kDefaultTuning[2];
   params.wide_prologue = kDefaultWidePrologue;

@@ -219,7 +219,12 @@ int neogemm_set_override(int cta_group, int block_n, int swap, int stream_k, int
  *          whole tiles (no cut tiles, no closing sums): -1 with tall tiles (256 rows per CTA
  *          sharing the small operand, one CTA per SM), 0 not at all (stream-K instead),
  *          1 with 128-row tiles, two CTAs per SM and half-size rings, whenever such a kernel
- *          exists and all tiles fit at once, 2 with tall tiles whenever they fit in one wave.
+ *          exists and all tiles fit at once, 2 with tall tiles whenever they fit in one wave,
+ *          3 and 4 as -1 with another way out for a tall tile's result (the default stages the
+ *          tile in the idle operand ring and stores it as one TMA box; pairs of 128-column tall
+ *          tiles also exchange the operands' roles in the MMA, so that no tensor work is spent
+ *          on rows past the tile's height): 4 keeps the usual roles, 3 also stores from
+ *          registers.
  *   key 8: wave pacing of launches with many waves of whole tiles (workers wait, briefly and
  *          without obligation, for each other at the start of every wave so that tiles sharing
  *          operand panels keep sharing them in L2): -1 from 8 waves on, 0 off, 1 from 2 waves on.

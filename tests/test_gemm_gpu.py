@@ -85,6 +85,42 @@ def test_tall_tiles_whole_wave(shape):
     assert ops.device_status()[0] == 0
 
 
+@pytest.mark.parametrize("shape", [(128, 28672, 2048), (96, 20008, 1024), (65, 29600, 1024),
+                                   (64, 28672, 1024), (16, 28672, 1024), (24, 20008, 1024),
+                                   (100, 30784, 1024)])
+def test_tall_tile_store_paths_agree(shape):
+    # A tall tile with a transposed bf16 result (row-major C, operands swapped) has three ways
+    # out: staged whole in the idle operand ring and stored by the TMA unit as one box (the
+    # default); the same with the operands' roles exchanged in the MMA, which the pair kernel of
+    # 128 columns does by default (the accumulator is then the transpose, one row of A per lane);
+    # and 16-byte stores from registers (what calls with unaligned outputs fall back to).
+    # All three must agree with the oracle and, bit for bit, with one another: every element
+    # sums the same products in the same k order.  Shapes: full and ragged last tiles (the TMA
+    # unit clips the box at the matrix edge; 20008 rows leave the last pair 136 + 16 of them),
+    # fewer rows of A than the pair's 2 x 64 (65: one row in the second CTA).
+    M, N, K = shape
+    A, B = make_problem(M, N, K, seed=17)
+    dA, dB = A.cuda(), B.cuda()
+    want = oracle.gemm_fp32(A, B)
+    outs = {}
+    for mode in (-1, 4, 3):
+        C = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        ops.set_tuning("two_ctas_per_sm", mode)
+        try:
+            ops.matmul(dA, dB, out=C)
+            cfg = ops.last_config()
+        finally:
+            ops.set_tuning("two_ctas_per_sm", -1)
+        torch.cuda.synchronize()
+        assert ops.device_status()[0] == 0, (mode, cfg)
+        assert cfg["stream_k"] == 0 and cfg["ctas"] == cfg["tiles"] * cfg["cta_group"], cfg
+        assert cfg["cta_group"] == (2 if M > 32 else 1), cfg
+        oracle.assert_parity(C, want, f"tall tile store mode {mode} {shape} {cfg}")
+        outs[mode] = C
+    for mode in (4, 3):
+        assert torch.equal(outs[-1].view(torch.int16), outs[mode].view(torch.int16)), mode
+
+
 @pytest.mark.parametrize("shape", [(16, 28672, 8192), (8, 19000, 1024), (24, 30000, 2048),
                                    (64, 28672, 4096), (40, 20008, 1536), (1, 37000, 1024),
                                    (100, 20000, 2048), (128, 28672, 1024)])
