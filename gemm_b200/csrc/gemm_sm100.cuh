@@ -703,6 +703,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
       if (lane != 0) timer_params.timers = nullptr;
       PhaseTimer wait_timer(timer_params), loop_timer(timer_params);
       loop_timer.begin();
+      int first_fill = 0;   // k-blocks issued so far, counted up to the ring's depth
       while (ok && it.next(seg, lane)) {
         if (p.pace_counter != nullptr && is_leader && seg_idx >= 1)
           pace_wave(p, seg_idx, num_workers, lane);
@@ -723,11 +724,19 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
         // tile, so results stay reproducible).
         const bool reverse_k = p.k_alternate != 0 && (seg_idx & 1) != 0 && seg.n_contrib == 1;
         for (int kb = seg.kb_begin; kb < kb_end; ++kb) {
-          wait_timer.begin();
-          const bool got = __all_sync(0xffffffffu,
-                                      mbar_wait(empty_bar + 8 * stage, phase ^ 1, abort_flag,
-                                                static_cast<uint32_t>(p.main_wait_hint_ns)));
-          wait_timer.end();
+          // The first pass over the ring finds every slot free: no MMA has read it yet, so
+          // there is nothing to wait for (a wait that passes at once still costs ~150 cycles,
+          // which a launch of a few k-blocks per CTA feels: it is the rate its loads go out at).
+          bool got = true;
+          if (Cfg::kNHalves == 2 || first_fill >= kStages) {
+            wait_timer.begin();
+            got = __all_sync(0xffffffffu,
+                             mbar_wait(empty_bar + 8 * stage, phase ^ 1, abort_flag,
+                                       static_cast<uint32_t>(p.main_wait_hint_ns)));
+            wait_timer.end();
+          } else {
+            ++first_fill;
+          }
           if (!got) {
             if (lane == 0)
               report_error(p, abort_flag, kDevTimeoutProducer, seg_idx, static_cast<int>(stage));
