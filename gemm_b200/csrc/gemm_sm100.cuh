@@ -180,7 +180,16 @@ struct GemmConfig {
   // result leaves as 16-byte vectors instead of 2-byte scalars.
   static constexpr int kDirectCols = (BLOCK_N >= 32) ? 32 : 16;
   static constexpr int SMEM_EPI_T_WARP = kDirectCols * 64;
+  // A tall tile is its CTA's only tile and stages in the operand ring, which is idle by then.
+  // What it needs behind the ring instead is room for its second MMA block to read: that block
+  // always spans rows 128..255 of a slot's X region, i.e. bytes up to 2 x SMEM_X_HALF from the
+  // slot's start, which for narrow tiles is more than a slot - past the LAST slot that would be
+  // past the CTA's shared memory, an illegal address.  (What is read there feeds accumulator
+  // lanes that are never stored.)
+  static constexpr int SMEM_TALL_PAD =
+      (kMHalves == 2 && 2 * SMEM_X_HALF > SMEM_STAGE) ? 2 * SMEM_X_HALF - SMEM_STAGE : 0;
   static constexpr int SMEM_EPI = (kEpiMode == kEpiTmaStore) ? kEpiWarps * kEpiBufs * SMEM_EPI_WARP_BUF
+                                  : (kMHalves == 2)          ? SMEM_TALL_PAD
                                                              : 4 * SMEM_EPI_T_WARP;
   static constexpr int SMEM_BARRIERS = (2 * kStages + 9) * 8 + 16;
   // +1024: the ring must start on a 1024-byte boundary for the 128-byte swizzle.
@@ -204,6 +213,8 @@ struct GemmConfig {
   static_assert(kCtaGroup == 1 || kTmemCols == 512,
                 "pair mode allocates all of tensor memory so both CTAs get column 0");
   static_assert(SMEM_TOTAL <= 232448, "exceeds 227 KB of shared memory per CTA");
+  static_assert(kMHalves == 1 || SMEM_STAGE + SMEM_EPI >= 2 * SMEM_X_HALF,
+                "the second MMA block of a tall tile reads 256 rows from a slot's start");
   static_assert(kMHalves == 1 || BLOCK_N * kTallRows * 2 <= kStages * SMEM_STAGE,
                 "a tall tile stages its whole result in the idle ring");
   static_assert(kMHalves == 1 || (kMHalves == 2 && kNHalves == 1 && kEpiMode == kEpiDirect &&
@@ -660,7 +671,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
   if (warp == 0 && lane == 0) {
     prefetch_tensormap(&tmap_x);
     prefetch_tensormap(&tmap_y);
-    if (Cfg::kEpiMode == kEpiTmaStore || (Cfg::kMHalves == 2 && (p.l2_hints & 32)))
+    if (Cfg::kEpiMode == kEpiTmaStore || (Cfg::kMHalves == 2 && (p.l2_hints & 96)))
       prefetch_tensormap(&tmap_d);
   }
   if (warp == 1) {
@@ -985,6 +996,12 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
     PhaseTimer wait_timer(timer_params), loop_timer(timer_params);
     loop_timer.begin();
     while (ok && it.next(seg, lane)) {
+      if (Cfg::kMHalves == 2 && seg_idx > 0) {
+        // A tall tile is its CTA's only tile (the launcher sizes the grid that way): its result
+        // is staged in the operand ring, which a second tile's loads would be filling.
+        if (lane == 0) report_error(p, abort_flag, kDevBounds, seg_idx, 9);
+        break;
+      }
       const uint32_t acc = (Cfg::kNHalves == 1) ? (seg_idx & 1) : 0;
       const uint32_t acc_phase = (Cfg::kNHalves == 1) ? ((seg_idx >> 1) & 1) : (seg_idx & 1);
       // Is this the CTA's last segment?  Then, once its accumulator is complete, nothing reads
@@ -1467,7 +1484,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
         // column are 128 contiguous bytes already.
         transposed = (p.out32 == nullptr) && (p.out_stride_r == 1) && ((p.out_stride_c & 7) == 0) &&
                      ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
-        const uint32_t stg = epi_base + (warp - 2) * Cfg::SMEM_EPI_T_WARP;
+        const uint32_t stg = (Cfg::kMHalves == 2 ? ring : epi_base) + (warp - 2) * Cfg::SMEM_EPI_T_WARP;
         // 32 columns per step where the tile has them: half as many dependent round trips to
         // the partials of a cut tile as with 16.
         constexpr int kDC = Cfg::kDirectCols;

@@ -865,15 +865,15 @@ int gemm_device(const void* A, const void* B, void* C, int64_t M, int64_t N, int
   }
   // Tuning key 7 = 3: tall tiles as by default, but stored from registers; 4: stored through the
   // TMA unit, but the pair kernel of 128 columns keeps the operands' usual roles.
-  const bool tall_tma = tall_tile_tma_store(plan, C, ldc, c_elem) && t_override.tuning[7] != 3;
-  const bool tall_flip = tall_tma && plan.cta_group == 2 && plan.block_n == 128 && !fusion.on &&
-                         t_override.tuning[7] != 4;
+  bool tall_tma = tall_tile_tma_store(plan, C, ldc, c_elem) && t_override.tuning[7] != 3;
+  bool tall_flip = tall_tma && plan.cta_group == 2 && plan.block_n == 128 && !fusion.on &&
+                   t_override.tuning[7] != 4;
   if (tall_tma) {
     rc = get_tensor_map(C, static_cast<uint64_t>(plan.Md), static_cast<uint64_t>(plan.Nd),
                         static_cast<uint64_t>(ldc) * 2,
                         tall_flip ? 64u : static_cast<uint32_t>(plan.block_n),
                         1000 + plan.tile_rows, &md);
-    if (rc != NEOGEMM_OK) return rc;
+    if (rc != NEOGEMM_OK) tall_tma = tall_flip = false;   // stores from registers serve any C
   }
 
   GemmParams params;
@@ -1634,14 +1634,14 @@ int neogemm_bf16_nt_noalloc(const void* A, const void* B, void* C, int64_t M, in
                              static_cast<uint64_t>(ldc) * 2, 32, 1, &md);
     if (rc != NEOGEMM_OK) return rc;
   }
-  const bool tall_tma = tall_tile_tma_store(plan, C, ldc, 2);
-  const bool tall_flip = tall_tma && plan.cta_group == 2 && plan.block_n == 128;
+  bool tall_tma = tall_tile_tma_store(plan, C, ldc, 2);
+  bool tall_flip = tall_tma && plan.cta_group == 2 && plan.block_n == 128;
   if (tall_tma) {
     rc = encode_map_uncached(C, static_cast<uint64_t>(plan.Md), static_cast<uint64_t>(plan.Nd),
                              static_cast<uint64_t>(ldc) * 2,
                              tall_flip ? 64u : static_cast<uint32_t>(plan.block_n),
                              1000 + plan.tile_rows, &md);
-    if (rc != NEOGEMM_OK) return rc;
+    if (rc != NEOGEMM_OK) tall_tma = tall_flip = false;   // stores from registers serve any C
   }
 
   GemmParams params;
