@@ -29,7 +29,7 @@ CASES = [  # (M, N, K): pair kernel, cut last wave, single-CTA TMA store, direct
     # whole tiles two CTAs to an SM
     (2048, 2048, 512), (4096, 4096, 1024), (520, 776, 264), (257, 250, 128), (16, 3584, 2048),
     (64, 28672, 1024), (24, 20000, 1024), (1024, 1024, 4096),   # the last: two-pass split-K
-    (128, 28672, 512),   # tall pair tiles of 128 columns: fused calls keep the usual operand roles
+    (128, 28672, 1024),   # tall pair tiles of 128 columns: fused calls keep the usual operand roles
 ]
 
 

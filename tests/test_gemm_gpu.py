@@ -87,7 +87,8 @@ def test_tall_tiles_whole_wave(shape):
 
 @pytest.mark.parametrize("shape", [(128, 28672, 2048), (96, 20008, 1024), (65, 29600, 1024),
                                    (64, 28672, 1024), (16, 28672, 1024), (24, 20008, 1024),
-                                   (100, 30784, 1024)])
+                                   (100, 30784, 1024), (96, 20008, 1000), (128, 19000, 8192),
+                                   (128, 19048, 1024), (80, 18952, 1024)])
 def test_tall_tile_store_paths_agree(shape):
     # A tall tile with a transposed bf16 result (row-major C, operands swapped) has three ways
     # out: staged whole in the idle operand ring and stored by the TMA unit as one box (the
@@ -97,7 +98,9 @@ def test_tall_tile_store_paths_agree(shape):
     # All three must agree with the oracle and, bit for bit, with one another: every element
     # sums the same products in the same k order.  Shapes: full and ragged last tiles (the TMA
     # unit clips the box at the matrix edge; 20008 rows leave the last pair 136 + 16 of them),
-    # fewer rows of A than the pair's 2 x 64 (65: one row in the second CTA).
+    # fewer rows of A than the pair's 2 x 64 (65: one row in the second CTA), a K that ends inside
+    # a k-block, tiles of the smallest height (19000 rows: 136 per CTA, a second MMA block of 8;
+    # 19048: 141 tiles, the last pair's second CTA has no rows at all; 18952: a last tile of 48).
     M, N, K = shape
     A, B = make_problem(M, N, K, seed=17)
     dA, dB = A.cuda(), B.cuda()
