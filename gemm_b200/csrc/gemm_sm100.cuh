@@ -1374,7 +1374,7 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
             // 0 .. tile_rows-1 of one CTA of the pair in columns 0 .. tile_rows-1 - for a
             // transposed result that is tile_rows x 2 contiguous bytes.  The lanes stage their
             // rows in the idle ring as [half of the lanes][64 rows of Y][tile_rows], 16 bytes
-            // at a time, and one thread hands each half to the TMA unit as one box.
+            // at a time, and each warp hands its 32 rows to the TMA unit as one box.
             const int m_local = row_in_cta & 63;
             const uint32_t owner = quad >> 1;
             const uint32_t pitch = static_cast<uint32_t>(p.tile_rows) * 2u;
@@ -1395,22 +1395,15 @@ gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_x,
                                pack_bf16x2(__uint_as_float(r[8 * v8 + 6]), __uint_as_float(r[8 * v8 + 7])));
               }
             }
+            // A warp's 32 rows of Y are a box of their own: no warp waits for another.
             fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive(epi_sync_bar);
-            if (warp == 2 && lane == 0) {
-              if (mbar_wait(epi_sync_bar, static_cast<uint32_t>(seg_idx & 1), abort_flag)) {
-                const int y = col0 + static_cast<int>(cta_rank) * 64;
-#pragma unroll 1
-                for (int o = 0; o < 2; ++o) {
-                  const int x = (tm * 2 + o) * p.tile_rows;
-                  if (x < p.Md && y < p.Nd)
-                    tma_store_2d(&tmap_d, ring + static_cast<uint32_t>(o) * (64u * pitch), x, y);
-                }
-                tma_store_commit();
-              } else {
-                report_error(p, abort_flag, kDevTimeoutEpilogue, seg_idx, 7);
-              }
+            if (lane == 0) {
+              const int y = col0 + static_cast<int>(cta_rank) * 64 + static_cast<int>(quad & 1u) * 32;
+              const int x = (tm * 2 + static_cast<int>(owner)) * p.tile_rows;
+              if (x < p.Md && y < p.Nd)
+                tma_store_2d(&tmap_d, dst - lane * pitch, x, y);
+              tma_store_commit();
             }
             stored = true;
           }

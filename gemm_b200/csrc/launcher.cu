@@ -871,7 +871,7 @@ int gemm_device(const void* A, const void* B, void* C, int64_t M, int64_t N, int
   if (tall_tma) {
     rc = get_tensor_map(C, static_cast<uint64_t>(plan.Md), static_cast<uint64_t>(plan.Nd),
                         static_cast<uint64_t>(ldc) * 2,
-                        tall_flip ? 64u : static_cast<uint32_t>(plan.block_n),
+                        tall_flip ? 32u : static_cast<uint32_t>(plan.block_n),
                         1000 + plan.tile_rows, &md);
     if (rc != NEOGEMM_OK) tall_tma = tall_flip = false;   // stores from registers serve any C
   }
@@ -1639,7 +1639,7 @@ int neogemm_bf16_nt_noalloc(const void* A, const void* B, void* C, int64_t M, in
   if (tall_tma) {
     rc = encode_map_uncached(C, static_cast<uint64_t>(plan.Md), static_cast<uint64_t>(plan.Nd),
                              static_cast<uint64_t>(ldc) * 2,
-                             tall_flip ? 64u : static_cast<uint32_t>(plan.block_n),
+                             tall_flip ? 32u : static_cast<uint32_t>(plan.block_n),
                              1000 + plan.tile_rows, &md);
     if (rc != NEOGEMM_OK) tall_tma = tall_flip = false;   // stores from registers serve any C
   }
