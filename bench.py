@@ -319,6 +319,7 @@ def run_extra_config(name, launches, seed, device, peaks, ops, roofline, traffic
                     for i in range(launches)]
     ours_calls[0]()
     cfg = ops.last_config()
+    cfg["store_path"] = ops.last_store_path()   # 1 / 2: a tall tile left as one TMA box
     replays = 5
     t_ours = time_graph(ours_calls, replays)
     t_cublas = time_graph(cublas_calls, replays)
@@ -471,6 +472,7 @@ def run_ours(args):
         step()
     torch.cuda.synchronize()
     cfg = ops.last_config()
+    cfg["store_path"] = ops.last_store_path()
 
     sampler = ClockSampler(local_rank)
     with sampler:

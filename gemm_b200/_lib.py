@@ -67,6 +67,8 @@ def _load() -> ctypes.CDLL:
     lib.neogemm_status_str.argtypes = [c_int]
     lib.neogemm_last_config.restype = c_int
     lib.neogemm_last_config.argtypes = [POINTER(c_int)]
+    lib.neogemm_last_store_path.restype = c_int
+    lib.neogemm_last_store_path.argtypes = []
     lib.neogemm_set_override.restype = c_int
     lib.neogemm_set_override.argtypes = [c_int] * 6
     lib.neogemm_set_tuning.restype = c_int

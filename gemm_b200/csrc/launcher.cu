@@ -178,6 +178,7 @@ struct Override {
 };
 thread_local Override t_override;
 thread_local int t_last_config[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+thread_local int t_last_store_path = 0;   // see neogemm_last_store_path
 thread_local long long* t_timers = nullptr;   // device buffer for phase timers, or null
 thread_local size_t t_timers_bytes = 0;
 
@@ -972,6 +973,7 @@ int gemm_device(const void* A, const void* B, void* C, int64_t M, int64_t N, int
     params.dyn_counter = reinterpret_cast<int*>(ws) + params.counters_len;
   }
 
+  t_last_store_path = tall_flip ? 2 : tall_tma ? 1 : 0;
   t_last_config[0] = plan.cta_group;
   t_last_config[1] = plan.block_n * plan.halves;
   t_last_config[2] = plan.kernel->stages;
@@ -1251,6 +1253,8 @@ int neogemm_last_config(int out[8]) {
   for (int i = 0; i < 8; ++i) out[i] = t_last_config[i];
   return NEOGEMM_OK;
 }
+
+int neogemm_last_store_path(void) { return t_last_store_path; }
 
 int neogemm_set_override(int cta_group, int block_n, int swap, int stream_k, int group_m,
                          int max_ctas) {
@@ -1691,6 +1695,7 @@ int neogemm_bf16_nt_noalloc(const void* A, const void* B, void* C, int64_t M, in
     params.partials_elems = static_cast<long long>(plan.partials_bytes / sizeof(float));
     params.dyn_counter = reinterpret_cast<int*>(st->scratch) + params.counters_len;
   }
+  t_last_store_path = tall_flip ? 2 : tall_tma ? 1 : 0;
   t_last_config[0] = plan.cta_group;
   t_last_config[1] = plan.block_n * plan.halves;
   t_last_config[2] = plan.kernel->stages;

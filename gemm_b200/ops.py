@@ -201,6 +201,12 @@ def last_config() -> dict:
     return dict(zip(keys, out))
 
 
+def last_store_path() -> int:
+    """0 regular epilogue, 1 tall tile stored as one TMA box, 2 the same with exchanged operand
+    roles (neogemm_last_store_path)."""
+    return int(lib.neogemm_last_store_path())
+
+
 def set_override(cta_group: int = -1, block_n: int = -1, swap: int = -1, stream_k: int = -1,
                  group_m: int = -1, max_ctas: int = -1) -> None:
     """Force parts of the kernel configuration on this thread (-1 = heuristic)."""
@@ -220,5 +226,5 @@ def set_tuning(key: str, value: int = -1) -> None:
 
 
 __all__ = ["neoGemmV1", "neogemm", "matmul", "matmul_fused", "linear", "matmul_host", "workspace_bytes",
-           "device_status", "clear_device_status", "last_config", "set_override", "set_tuning",
-           "NeoGemmError"]
+           "device_status", "clear_device_status", "last_config", "last_store_path", "set_override",
+           "set_tuning", "NeoGemmError"]

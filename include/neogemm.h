@@ -195,6 +195,13 @@ const char* neogemm_status_str(int status);
  * out[5] = CTAs launched, out[6] = tiles, out[7] = raster group height. */
 int neogemm_last_config(int out[8]);
 
+/* How the tiles of the most recent neogemm_bf16_nt*() call on this thread left the SMs:
+ * 0 the kernel's regular epilogue (TMA-store boxes of 32 rows, or stores from registers),
+ * 1 a tall tile staged whole in the idle operand ring and stored as one TMA box,
+ * 2 the same with the operands' roles exchanged in the MMA (pairs of 128-column tall tiles).
+ * For tests and benchmarks; no counterpart in the reference. */
+int neogemm_last_store_path(void);
+
 /* Tuning / test override for the calling thread; -1 leaves a field to the heuristic.
  *   cta_group: 1 or 2;  block_n: 16,32,64,128,256;  swap: 0/1;  stream_k: 0/1;
  *   group_m: raster group height in tiles;  max_ctas: cap on launched CTAs. */

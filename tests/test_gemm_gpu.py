@@ -40,6 +40,8 @@ def test_config_decode_shapes(M):
     stages = 7 if M <= 64 else 6
     assert (cfg["stream_k"], cfg["ctas"], cfg["tiles"], cfg["stages"], cfg["cta_group"]) == \
         (0, 144, 144 // group, stages, group), cfg
+    # the finished tile leaves as one TMA box; M=128 also with the operands' roles exchanged
+    assert ops.last_store_path() == (2 if M > 64 else 1)
     if group == 2:
         stats, cfg = run_case(M, 28672, 8192, override=dict(cta_group=1))
         assert (cfg["stream_k"], cfg["ctas"], cfg["tiles"], cfg["cta_group"]) == (0, 144, 144, 1), cfg
@@ -112,12 +114,14 @@ def test_tall_tile_store_paths_agree(shape):
         try:
             ops.matmul(dA, dB, out=C)
             cfg = ops.last_config()
+            path = ops.last_store_path()
         finally:
             ops.set_tuning("two_ctas_per_sm", -1)
         torch.cuda.synchronize()
         assert ops.device_status()[0] == 0, (mode, cfg)
         assert cfg["stream_k"] == 0 and cfg["ctas"] == cfg["tiles"] * cfg["cta_group"], cfg
         assert cfg["cta_group"] == (2 if M > 32 else 1), cfg
+        assert path == {-1: 2 if M > 64 else 1, 4: 1, 3: 0}[mode], (mode, path, cfg)
         oracle.assert_parity(C, want, f"tall tile store mode {mode} {shape} {cfg}")
         outs[mode] = C
     for mode in (4, 3):
